@@ -9,6 +9,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "lib", "libcrabml_cuda.so")
 HEADER = os.path.join(os.path.dirname(HERE), "include", "crabml_cuda.h")
 RUNNER_HEADER = os.path.join(os.path.dirname(HERE), "include", "crabml_runner.h")
+SEQOPS_HEADER = os.path.join(os.path.dirname(HERE), "include", "crabml_seqops.h")
+ZATORAX_HEADER = os.path.join(os.path.dirname(HERE), "include", "crabml_zatorax.h")
 
 CC_OK, CC_ERR_TENSOR, CC_ERR_CUDA, CC_ERR_ARG, CC_ERR_UNSUPPORTED = 0, 1, 2, 3, 4
 CC_MAX_DIMS = 4
@@ -16,6 +18,8 @@ CC_MAX_DIMS = 4
 # GGMLType ids (crabml-core/src/gguf.rs:86-108)
 F32, F16, Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q8_1 = 0, 1, 2, 3, 6, 7, 8, 9
 Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, Q8_K = 10, 11, 12, 13, 14, 15
+I32, BF16 = 26, 30
+ACT_NONE, ACT_SILU, ACT_GELU_TANH = 0, 1, 2
 ROPE_LLAMA, ROPE_NEOX = 0, 1
 
 
@@ -39,9 +43,9 @@ class cc_device_options(C.Structure):
 def declared_symbols():
     """Every CC_API prototype name in the headers (used by the CPU-side export test)."""
     out = []
-    for h in (HEADER, RUNNER_HEADER):
+    for h in (HEADER, RUNNER_HEADER, SEQOPS_HEADER, ZATORAX_HEADER):
         with open(h) as f:
-            out += re.findall(r"^CC_API [\w\s\*]+?\b(ccr?_\w*)\(", f.read(), flags=re.M)
+            out += re.findall(r"^CC_API [\w\s\*]+?\b(c[cz]r?_\w*)\(", f.read(), flags=re.M)
     return out
 
 
@@ -56,6 +60,23 @@ class ccr_llama_weights(C.Structure):
     _fields_ = [("token_embed", C.c_void_p), ("wq", _pp), ("wk", _pp), ("wv", _pp), ("wo", _pp), ("ffn_gate", _pp),
                 ("ffn_down", _pp), ("ffn_up", _pp), ("rms_att", _pp), ("rms_ffn", _pp), ("rms_final", C.c_void_p),
                 ("output_weight", C.c_void_p), ("bq", _pp), ("bk", _pp), ("bv", _pp)]
+
+
+class czr_layer_config(C.Structure):            # include/crabml_zatorax.h
+    _fields_ = [(n, C.c_int32) for n in ("mixer", "heads", "kv_heads", "dim", "vdim", "conv", "window", "kv_from")] + [("scale", C.c_float)] + \
+               [(n, C.c_int32) for n in ("has_mlp", "experts", "top", "groups", "keep_groups", "expert_ff", "shared_ff")]
+
+
+class czr_config(C.Structure):
+    _fields_ = [("n_layers", C.c_int32), ("width", C.c_int32), ("vocab", C.c_int32), ("norm_eps", C.c_float), ("chunk", C.c_int32)]
+
+
+CZR_WEIGHT_FIELDS = ("norm1", "norm2", "q", "k", "v", "o", "q_conv", "k_conv", "v_conv", "b", "a", "a_log", "dt_bias", "out_norm", "g", "q_norm", "k_norm",
+                     "r1", "r2", "router", "correction", "e_gate", "e_up", "e_down", "s_gate", "s_up", "s_down")
+
+
+class czr_layer_weights(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in CZR_WEIGHT_FIELDS]
 
 
 _lib = None
@@ -146,6 +167,29 @@ def load_library(build_if_missing: bool = True):
         "cc_tensor_export_f32_async": (i32, [vp, pv, vp, C.c_size_t]),
         "cc_host_alloc": (i32, [vp, C.c_size_t, pp]),
         "cc_host_free": (None, [vp, vp]),
+    })
+    # sequence-mixing / routing ops (include/crabml_seqops.h) and the Zatorax runner (include/crabml_zatorax.h)
+    sig.update({
+        "cc_tensor_zero": (i32, [vp, pv]),
+        "cc_rms_norm_gain": (i32, [vp, pv, pv, pv, f32, i32]),
+        "cc_gated_head_rms_norm": (i32, [vp, pv, pv, pv, i32, f32, i32]),
+        "cc_glu_inplace": (i32, [vp, pv, pv, i32]),
+        "cc_short_conv": (i32, [vp, pv, pv, pv, i32, i32, i32, f32, f32, pp]),
+        "cc_gated_delta_rule": (i32, [vp, pv, pv, pv, pv, pv, pv, pv, pv, i32, i32, i32, i32, pp]),
+        "cc_kv_ring_append": (i32, [vp, pv, pv, pv, pv, pv, f32, i64, i32, i32, i32]),
+        "cc_window_attention": (i32, [vp, pv, pv, f32, pv, pv, i64, i32, i32, i32, i32, i32, f32, pv, pv, pp]),
+        "cc_moe_route": (i32, [vp, pv, pv, pv, i32, i32, i32, i32, pp, pp]),
+        "cc_moe_experts": (i32, [vp, pv, pv, pv, pv, pv, pv, i32, i32, i32, pp]),
+        "czr_runner_create": (i32, [vp, C.POINTER(czr_config), C.POINTER(czr_layer_config), C.POINTER(czr_layer_weights), vp, vp, vp, pp]),
+        "czr_last_create_error": (C.c_char_p, []),
+        "czr_runner_destroy": (None, [vp]),
+        "czr_runner_last_error": (C.c_char_p, [vp]),
+        "czr_seq_open": (i32, [vp, C.POINTER(i32)]),
+        "czr_seq_close": (i32, [vp, i32]),
+        "czr_seq_len": (i64, [vp, i32]),
+        "czr_runner_stats": (i32, [vp, C.POINTER(i64)]),
+        "czr_runner_step": (i32, [vp, i32, C.POINTER(i64), i32, C.POINTER(i32), i32, vp]),
+        "czr_runner_generate_greedy": (i32, [vp, i32, C.POINTER(i64), i32, i32, i64, C.POINTER(i64), C.POINTER(i32)]),
     })
     for name, (res, args) in sig.items():
         fn = getattr(L, name)

@@ -219,6 +219,10 @@ bool cc_prefill_supported(int wtype, int64_t m, int64_t k, int64_t b);
 int cc_launch_prefill_matmul(cc_device* dev, const cc_buf* w, const void* act, const float* x_f32, float* out, int64_t m, int64_t k, int64_t b);
 void cc_prefill_release(cc_device* dev);
 
+// ---- dense.cu: plain F32 / BF16 weight matrices with a batch of activation rows -------------------
+bool cc_dense_supported(int wtype, int64_t b);
+int cc_launch_dense(cc_device* dev, const cc_buf* w, const float* x_f32, float* out, int64_t m, int64_t k, int64_t b);
+
 // ---- ops.cu --------------------------------------------------------------------------------------
 int cc_launch_rms_norm(cc_device* dev, float* x, int64_t rows, int64_t cols, float eps);
 int cc_launch_softmax(cc_device* dev, float* x, int64_t rows, int64_t cols);

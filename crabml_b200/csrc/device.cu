@@ -21,7 +21,7 @@ int cc_fail(cc_device* dev, int code, const char* fmt, ...) {
 // ---- type facts (crabml-core/src/gguf.rs:86-108; block sizes SURVEY Appendix A) ------------------
 int cc_block_elems(int t) {
     switch (t) {
-    case CC_F32: case CC_F16: return 1;
+    case CC_F32: case CC_F16: case CC_BF16: case CC_I32: return 1;
     case CC_Q4_0: case CC_Q4_1: case CC_Q5_0: case CC_Q5_1: case CC_Q8_0: case CC_Q8_1: return 32;
     case CC_Q2_K: case CC_Q3_K: case CC_Q4_K: case CC_Q5_K: case CC_Q6_K: case CC_Q8_K: return 256;
     }
@@ -29,7 +29,7 @@ int cc_block_elems(int t) {
 }
 size_t cc_block_bytes(int t) {
     switch (t) {
-    case CC_F32: return 4; case CC_F16: return 2;
+    case CC_F32: case CC_I32: return 4; case CC_F16: case CC_BF16: return 2;
     case CC_Q4_0: return 18; case CC_Q4_1: return 20; case CC_Q5_0: return 22; case CC_Q5_1: return 24;
     case CC_Q8_0: return 34; case CC_Q8_1: return 36;
     case CC_Q2_K: return 84; case CC_Q3_K: return 110; case CC_Q4_K: return 144; case CC_Q5_K: return 176;
@@ -39,7 +39,7 @@ size_t cc_block_bytes(int t) {
 }
 int cc_partner_type(int t) {   // buf/api.rs:142-159
     switch (t) {
-    case CC_F32: return CC_F32; case CC_F16: return CC_F16;
+    case CC_F32: case CC_BF16: return CC_F32; case CC_F16: return CC_F16;      // BF16 weights take the f32 activation and round it themselves
     case CC_Q8_0: case CC_Q4_0: case CC_Q5_0: return CC_Q8_0;
     case CC_Q8_1: case CC_Q4_1: case CC_Q5_1: return CC_Q8_1;
     case CC_Q2_K: case CC_Q3_K: case CC_Q4_K: case CC_Q5_K: case CC_Q6_K: case CC_Q8_K: return CC_Q8_K;
@@ -207,7 +207,7 @@ void cc_pool_free(cc_device* dev, void* p, size_t cls) {
 }
 
 int cc_new_activation(cc_device* dev, int64_t nelems, int dtype, bool zero, cc_buf** out) {
-    size_t esz = dtype == CC_F32 ? 4 : 2;
+    size_t esz = (dtype == CC_F32 || dtype == CC_I32) ? 4 : 2;
     void* p = nullptr;
     size_t cls = 0;
     int rc = cc_pool_alloc(dev, (size_t)nelems * esz, &p, &cls);

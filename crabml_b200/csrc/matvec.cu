@@ -55,6 +55,7 @@ int cc_launch_matvec(cc_device* dev, const cc_buf* w, const void* act, const flo
     switch (w->dtype) {
     case CC_F32: return launch<TF32>(dev, w, x_f32, n_total, out, m, k, b);
     case CC_F16: return launch<TF16>(dev, w, act, n_total, out, m, k, b);
+    case CC_BF16: return launch<TBF16>(dev, w, x_f32, n_total, out, m, k, b);
     case CC_Q8_0: return launch<TQ8_0>(dev, w, act, n_total, out, m, k, b);
     case CC_Q4_0: return launch<TQ4_0>(dev, w, act, n_total, out, m, k, b);
     case CC_Q5_0: return launch<TQ5_0>(dev, w, act, n_total, out, m, k, b);

@@ -19,6 +19,8 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <cuda_bf16.h>
+
 #include "common.cuh"
 #include "dequant.cuh"
 
@@ -69,9 +71,9 @@ __device__ __forceinline__ uint64_t pg_smem_desc(unsigned smem_addr) {
     return d;
 }
 // instruction descriptor of kind::f16: f32 accumulator, f16 A and B, both K-major, dense
-__host__ __device__ constexpr unsigned pg_instr_desc(int umma_m, int umma_n) {
+__host__ __device__ constexpr unsigned pg_instr_desc(int umma_m, int umma_n, int fmt = 0) {
     return (1u << 4)                          // bits [4, 6): accumulator format, 1 = F32
-           | (0u << 7) | (0u << 10)           // bits [7, 10) / [10, 13): A / B format, 0 = F16
+           | ((unsigned)fmt << 7) | ((unsigned)fmt << 10)   // bits [7, 10) / [10, 13): A / B format, 0 = F16, 1 = BF16
            | (0u << 15) | (0u << 16)          // A / B major: 0 = K-major
            | ((unsigned)(umma_n >> 3) << 17)  // bits [17, 23): N >> 3
            | ((unsigned)(umma_m >> 4) << 24); // bits [24, 29): M >> 4
@@ -86,7 +88,7 @@ struct PgShared {
 // MT = 2: the CTA owns a 256-row weight tile as TWO M = 128 accumulators (2 x BLOCK_N TMEM columns) that share every B tile -- 1.5x
 // fewer operand bytes per FLOP than 128 x 256 tiles, which matters because 148 CTAs pulling 48 KB per 128x256x64 step ask more of L2
 // than it delivers (profiles/r02e: 47 % tensor pipe with MT = 1).
-template <int BLOCK_N, int MT>
+template <int BLOCK_N, int MT, int FMT = 0>
 __global__ void __launch_bounds__(PG_THREADS, 1) umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                                                                   float* __restrict__ C, int m, int b, int k) {
     extern __shared__ __align__(1024) uint8_t pg_smem_raw[];
@@ -135,7 +137,7 @@ __global__ void __launch_bounds__(PG_THREADS, 1) umma_gemm_kernel(const __grid_c
     } else if (warp == 1) {
         // ===== MMA issuer: a single thread =====
         if (lane == 0) {
-            constexpr unsigned idesc = pg_instr_desc(PG_BLOCK_M, BLOCK_N);
+            constexpr unsigned idesc = pg_instr_desc(PG_BLOCK_M, BLOCK_N, FMT);
             for (int kb = 0; kb < num_kb; kb++) {
                 const int s = kb % STAGES;
                 const unsigned ph = (unsigned)(kb / STAGES) & 1u;
@@ -244,14 +246,14 @@ static PFN_encodeTiled pg_encode() {
     return fn;
 }
 // f16 matrix [rows][k] (k contiguous), box = 64 columns x box_rows rows, 128-byte swizzle, out-of-bounds rows read as zero
-static int pg_make_tmap(cc_device* dev, CUtensorMap* tm, const void* base, int64_t rows, int64_t k, int box_rows) {
+static int pg_make_tmap(cc_device* dev, CUtensorMap* tm, const void* base, int64_t rows, int64_t k, int box_rows, bool bf16 = false) {
     PFN_encodeTiled enc = pg_encode();
     if (!enc) return cc_fail(dev, CC_ERR_CUDA, "prefill: cuTensorMapEncodeTiled is not available from this driver");
     cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)k * 2};
     cuuint32_t box[2] = {PG_BLOCK_K, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+    CUresult r = enc(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cc_fail(dev, CC_ERR_CUDA, "prefill: cuTensorMapEncodeTiled failed (%d)", (int)r);
     return CC_OK;
@@ -286,14 +288,14 @@ bool cc_prefill_supported(int wtype, int64_t m, int64_t k, int64_t b) {
     return b >= min_b && k % PG_BLOCK_K == 0 && k >= PG_BLOCK_K && m >= 1 && (at == CC_Q8_0 || at == CC_Q8_K);
 }
 
-template <int BLOCK_N, int MT>
+template <int BLOCK_N, int MT, int FMT = 0>
 static int pg_launch(cc_device* dev, const CUtensorMap& tw, const CUtensorMap& tx, float* out, int64_t m, int64_t b, int64_t k) {
     const size_t stage = (size_t)MT * PG_BLOCK_M * PG_BLOCK_K * 2 + (size_t)BLOCK_N * PG_BLOCK_K * 2;
     const int stages = stage * PG_STAGES <= 200 * 1024 ? PG_STAGES : 3;
     const size_t smem = (size_t)stages * stage + 1024;
-    CC_CUDA(dev, cudaFuncSetAttribute(umma_gemm_kernel<BLOCK_N, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CC_CUDA(dev, cudaFuncSetAttribute(umma_gemm_kernel<BLOCK_N, MT, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((unsigned)((m + PG_BLOCK_M * MT - 1) / (PG_BLOCK_M * MT)), (unsigned)((b + BLOCK_N - 1) / BLOCK_N));
-    umma_gemm_kernel<BLOCK_N, MT><<<grid, PG_THREADS, smem, dev->stream>>>(tw, tx, out, (int)m, (int)b, (int)k);
+    umma_gemm_kernel<BLOCK_N, MT, FMT><<<grid, PG_THREADS, smem, dev->stream>>>(tw, tx, out, (int)m, (int)b, (int)k);
     CC_LAUNCH_CHECK(dev);
     return CC_OK;
 }
@@ -347,4 +349,34 @@ int cc_launch_prefill_matmul(cc_device* dev, const cc_buf* w, const void* act_q8
     if (block_n == 256) return mt2 ? pg_launch<256, 2>(dev, tw, tx, out, m, b, k) : pg_launch<256, 1>(dev, tw, tx, out, m, b, k);
     if (block_n == 128) return mt2 ? pg_launch<128, 2>(dev, tw, tx, out, m, b, k) : pg_launch<128, 1>(dev, tw, tx, out, m, b, k);
     return mt2 ? pg_launch<64, 2>(dev, tw, tx, out, m, b, k) : pg_launch<64, 1>(dev, tw, tx, out, m, b, k);
+}
+
+// ---- plain bfloat16 weights (dense.cu): the weight matrix [m][k] is its own tile source, the f32 activation rows are rounded to
+// bfloat16 once, and the same pipeline runs with the bf16 operand format ---------------------------------------------------------------
+__global__ void act_f32_to_bf16_kernel(const float* __restrict__ x, int64_t nelems, __nv_bfloat16* __restrict__ out) {
+    const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+    if (i >= nelems) return;
+    *(__nv_bfloat162*)(out + i) = __floats2bfloat162_rn(x[i], x[i + 1]);
+}
+bool cc_prefill_bf16_supported(int64_t m, int64_t k, int64_t b) {
+    static const bool off = getenv("CRABML_PREFILL_OFF") != nullptr;
+    return !off && b >= 32 && m >= 1 && k >= PG_BLOCK_K && k % PG_BLOCK_K == 0;
+}
+int cc_launch_prefill_bf16(cc_device* dev, const cc_buf* w, const float* x_f32, float* out, int64_t m, int64_t k, int64_t b) {
+    PgScratch* s = pg_scratch(dev);
+    int rc = pg_ensure(dev, &s->x, &s->x_bytes, (size_t)b * k * 2);
+    if (rc) return rc;
+    const int64_t na = b * k;
+    act_f32_to_bf16_kernel<<<(unsigned)((na / 2 + 255) / 256), 256, 0, dev->stream>>>(x_f32, na, (__nv_bfloat16*)s->x);
+    CC_LAUNCH_CHECK(dev);
+    const int block_n = b >= 192 ? 256 : b >= 96 ? 128 : 64;
+    CUtensorMap tw, tx;
+    rc = pg_make_tmap(dev, &tw, w->plane[0], m, k, PG_BLOCK_M, true);
+    if (rc) return rc;
+    rc = pg_make_tmap(dev, &tx, s->x, b, k, block_n, true);
+    if (rc) return rc;
+    const bool mt2 = m >= 512;
+    if (block_n == 256) return mt2 ? pg_launch<256, 2, 1>(dev, tw, tx, out, m, b, k) : pg_launch<256, 1, 1>(dev, tw, tx, out, m, b, k);
+    if (block_n == 128) return mt2 ? pg_launch<128, 2, 1>(dev, tw, tx, out, m, b, k) : pg_launch<128, 1, 1>(dev, tw, tx, out, m, b, k);
+    return mt2 ? pg_launch<64, 2, 1>(dev, tw, tx, out, m, b, k) : pg_launch<64, 1, 1>(dev, tw, tx, out, m, b, k);
 }

@@ -1,0 +1,424 @@
+// seqops.cu -- sequence-mixing and normalisation ops of include/crabml_seqops.h: norms on the sublayer output, the short causal
+// convolution, the gated delta rule, and sliding-window attention over a ring cache.  Everything here is computed in 32-bit floats
+// (explicit fmaf; expf / logf / log1pf of the CUDA math library, not the fast intrinsics).
+//
+// One property every kernel keeps: the value computed for a token depends only on that token's inputs and on the state / cache
+// contents, never on how many tokens the call carries or where the token sits in the call.  Sums run in a fixed order per output
+// (a warp's lane-strided partial sums and the xor butterfly, or one thread's sequential loop), so prefill, chunked prefill and
+// token-by-token decoding give the same bits for the recurrent layers and the same bits per (query, key set) for attention.
+#include <cuda_bf16.h>
+
+#include "../../include/crabml_seqops.h"
+#include "capi_checks.cuh"
+
+#define SEQ_ENTER(dev, what)                                                                                          \
+    if (!(dev)) return CC_ERR_ARG;                                                                                    \
+    CC_ENTER(dev);                                                                                                    \
+    if (LAZY(dev)) return cc_fail((dev), CC_ERR_UNSUPPORTED, "%s: not available on a lazy (graph / megakernel) device", what)
+#define SEQ_VIEW(dev, v, what)                                                                                        \
+    do {                                                                                                              \
+        if (!view_ok(v)) return cc_fail((dev), CC_ERR_ARG, "%s: bad tensor view", what);                              \
+        if (!view_in_bounds(v)) return cc_fail((dev), CC_ERR_TENSOR, "%s: view addresses element %lld of a buffer of %lld", what, \
+                                               (long long)view_max_offset(v), (long long)(v)->buf->nelems);           \
+        CC_REQUIRE(dev, view_contiguous(v), "%s: not contiguous", what);                                              \
+    } while (0)
+#define SEQ_F32(dev, v, what)                \
+    do {                                     \
+        SEQ_VIEW(dev, v, what);              \
+        REQUIRE_F32(dev, v, what);           \
+    } while (0)
+static inline float* fptr(const cc_view* v) { return (float*)v->buf->plane[0]; }
+
+__device__ __forceinline__ float seq_silu(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float seq_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float seq_softplus(float z) { return fmaxf(z, 0.0f) + log1pf(expf(-fabsf(z))); }
+__device__ __forceinline__ float seq_gelu_tanh(float z) { return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
+__device__ __forceinline__ float seq_act(float z, int act) { return act == CC_ACT_SILU ? seq_silu(z) : act == CC_ACT_GELU_TANH ? seq_gelu_tanh(z) : z; }
+
+extern "C" CC_API int cc_tensor_zero(cc_device* dev, const cc_view* x) {
+    SEQ_ENTER(dev, "tensor_zero");
+    SEQ_VIEW(dev, x, "tensor_zero");
+    const size_t esz = cc_block_bytes(x->buf->dtype);
+    CC_REQUIRE(dev, !cc_is_quant(x->buf->dtype), "tensor_zero: plain types only");
+    if (view_len(x)) CC_CUDA(dev, cudaMemsetAsync(x->buf->plane[0], 0, (size_t)view_len(x) * esz, dev->stream));
+    return CC_OK;
+}
+
+// ---- norms --------------------------------------------------------------------------------------------------------------------
+// one warp per row: lane-strided sum of squares, butterfly, then the scaled write
+__global__ void rms_norm_gain_kernel(float* __restrict__ dst, const float* __restrict__ y, const float* __restrict__ gain, int gain_n, int rows, int cols,
+                                     float eps, int accumulate) {
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (r >= rows) return;
+    const float* yr = y + (int64_t)r * cols;
+    float ss = 0.0f;
+    for (int c = lane; c < cols; c += 32) ss = fmaf(yr[c], yr[c], ss);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)cols + eps);
+    float* dr = dst + (int64_t)r * cols;
+    for (int c = lane; c < cols; c += 32) {
+        const float v = yr[c] * inv * gain[gain_n == 1 ? 0 : c];
+        dr[c] = accumulate ? dr[c] + v : v;
+    }
+}
+extern "C" CC_API int cc_rms_norm_gain(cc_device* dev, const cc_view* dst, const cc_view* y, const cc_view* gain, float eps, int32_t accumulate) {
+    SEQ_ENTER(dev, "rms_norm_gain");
+    SEQ_F32(dev, dst, "rms_norm_gain dst"); SEQ_F32(dev, y, "rms_norm_gain y"); SEQ_F32(dev, gain, "rms_norm_gain gain");
+    CC_REQUIRE(dev, dst->ndim == 2 && y->ndim == 2 && dst->shape[0] == y->shape[0] && dst->shape[1] == y->shape[1], "rms_norm_gain: dst and y must be [rows, cols]");
+    const int64_t rows = y->shape[0], cols = y->shape[1], gn = view_len(gain);
+    CC_REQUIRE(dev, gn == 1 || gn == cols, "rms_norm_gain: gain has %lld elements, need 1 or %lld", (long long)gn, (long long)cols);
+    if (rows == 0) return CC_OK;
+    rms_norm_gain_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, dev->stream>>>(fptr(dst), fptr(y), fptr(gain), (int)gn, (int)rows, (int)cols, eps, accumulate);
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}
+
+// one warp per (row, head)
+__global__ void gated_head_rms_norm_kernel(float* __restrict__ x, const float* __restrict__ gate, const float* __restrict__ w, int64_t n_units, int hs, float eps, int act) {
+    const int64_t u = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (u >= n_units) return;
+    float* xr = x + u * hs;
+    const float* gr = gate + u * hs;
+    float ss = 0.0f;
+    for (int c = lane; c < hs; c += 32) ss = fmaf(xr[c], xr[c], ss);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)hs + eps);
+    for (int c = lane; c < hs; c += 32) xr[c] = xr[c] * inv * w[c] * seq_act(gr[c], act);
+}
+extern "C" CC_API int cc_gated_head_rms_norm(cc_device* dev, const cc_view* x, const cc_view* gate, const cc_view* w, int32_t head_size, float eps, int32_t gate_act) {
+    SEQ_ENTER(dev, "gated_head_rms_norm");
+    SEQ_F32(dev, x, "gated_head_rms_norm x"); SEQ_F32(dev, gate, "gated_head_rms_norm gate"); SEQ_F32(dev, w, "gated_head_rms_norm w");
+    const int64_t n = view_len(x);
+    CC_REQUIRE(dev, head_size > 0 && n % head_size == 0 && view_len(gate) == n && view_len(w) == head_size, "gated_head_rms_norm: shapes do not fit head_size %d", head_size);
+    const int64_t units = n / head_size;
+    if (!units) return CC_OK;
+    gated_head_rms_norm_kernel<<<(unsigned)((units + 7) / 8), 256, 0, dev->stream>>>(fptr(x), fptr(gate), fptr(w), units, head_size, eps, gate_act);
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}
+
+__global__ void glu_kernel(float* __restrict__ g, const float* __restrict__ u, int64_t n, int act) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) g[i] = seq_act(g[i], act) * u[i];
+}
+extern "C" CC_API int cc_glu_inplace(cc_device* dev, const cc_view* gate, const cc_view* up, int32_t act) {
+    SEQ_ENTER(dev, "glu_inplace");
+    SEQ_F32(dev, gate, "glu_inplace gate"); SEQ_F32(dev, up, "glu_inplace up");
+    const int64_t n = view_len(gate);
+    CC_REQUIRE(dev, view_len(up) == n, "glu_inplace: sizes differ");
+    if (!n) return CC_OK;
+    glu_kernel<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>(fptr(gate), fptr(up), n, act);
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}
+
+// ---- short causal convolution ----------------------------------------------------------------------------------------------------
+// one warp per (token, run of hs channels).  in[t'] for t' < 0 comes from the tail: tail row (K-1) + t'.
+__global__ void short_conv_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ tail, float* __restrict__ y, int T, int C,
+                                  int K, int hs, int act, int unit, float ueps, float uscale) {
+    const int heads = C / hs;
+    const int64_t u = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (u >= (int64_t)T * heads) return;
+    const int t = (int)(u / heads), h = (int)(u % heads);
+    float ss = 0.0f;
+    for (int cc = lane; cc < hs; cc += 32) {
+        const int c = h * hs + cc;
+        float acc = 0.0f;
+        for (int j = 0; j < K; j++) {
+            const int ti = t - (K - 1) + j;
+            const float v = ti >= 0 ? x[(int64_t)ti * C + c] : tail[(int64_t)(ti + K - 1) * C + c];
+            acc = fmaf(w[(int64_t)c * K + j], v, acc);
+        }
+        acc = seq_act(acc, act);
+        y[(int64_t)t * C + c] = acc;
+        ss = fmaf(acc, acc, ss);
+    }
+    if (unit) {
+        ss = warp_sum(ss);
+        const float f = uscale / sqrtf(ss + ueps);
+        for (int cc = lane; cc < hs; cc += 32) y[(int64_t)t * C + h * hs + cc] *= f;
+    }
+}
+// tail <- the last K-1 rows of (tail ++ x); one thread per channel, ascending rows: row j is written after row T + j > j was read
+__global__ void short_conv_tail_kernel(const float* __restrict__ x, float* __restrict__ tail, int T, int C, int K) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    for (int j = 0; j < K - 1; j++) {
+        const int ti = T + j - (K - 1);
+        tail[(int64_t)j * C + c] = ti >= 0 ? x[(int64_t)ti * C + c] : tail[(int64_t)(ti + K - 1) * C + c];
+    }
+}
+extern "C" CC_API int cc_short_conv(cc_device* dev, const cc_view* x, const cc_view* w, const cc_view* tail, int32_t act, int32_t head_size, int32_t unit_norm,
+                                    float unit_eps, float unit_scale, cc_buf** out) {
+    SEQ_ENTER(dev, "short_conv");
+    if (!out) return cc_fail(dev, CC_ERR_ARG, "short_conv: out is NULL");
+    SEQ_F32(dev, x, "short_conv x"); SEQ_F32(dev, w, "short_conv w");
+    CC_REQUIRE(dev, x->ndim == 2 && w->ndim == 2 && w->shape[0] == x->shape[1], "short_conv: x must be [T, C] and w [C, K]");
+    const int64_t T = x->shape[0], C = x->shape[1], K = w->shape[1];
+    CC_REQUIRE(dev, K >= 1, "short_conv: no taps");
+    if (K > 1) {
+        SEQ_F32(dev, tail, "short_conv tail");
+        CC_REQUIRE(dev, view_len(tail) == (K - 1) * C, "short_conv: tail must be [K-1, C]");
+    }
+    const int hs = head_size > 0 ? head_size : (int)C;
+    CC_REQUIRE(dev, C % hs == 0, "short_conv: head_size %d does not divide %lld channels", hs, (long long)C);
+    cc_buf* y = nullptr;
+    int rc = cc_new_activation(dev, T * C, CC_F32, false, &y);
+    if (rc) return rc;
+    *out = y;
+    if (T == 0) return CC_OK;
+    const float* tp = K > 1 ? fptr(tail) : nullptr;
+    const int64_t units = T * (C / hs);
+    short_conv_kernel<<<(unsigned)((units + 7) / 8), 256, 0, dev->stream>>>(fptr(x), fptr(w), tp, (float*)y->base, (int)T, (int)C, (int)K, hs, act, unit_norm, unit_eps, unit_scale);
+    CC_LAUNCH_CHECK(dev);
+    if (K > 1) {
+        short_conv_tail_kernel<<<(unsigned)((C + 127) / 128), 128, 0, dev->stream>>>(fptr(x), fptr(tail), (int)T, (int)C, (int)K);
+        CC_LAUNCH_CHECK(dev);
+    }
+    return CC_OK;
+}
+
+// ---- gated delta rule -------------------------------------------------------------------------------------------------------------
+// beta / decay of every (token, head): bd[(t * H + h) * 2] = {sigmoid(b), exp(-exp(a_log) * softplus(a + dt_bias))}
+__global__ void delta_gates_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                                   float* __restrict__ bd, int64_t n, int H) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int h = (int)(i % H);
+    bd[i * 2] = seq_sigmoid(b[i]);
+    bd[i * 2 + 1] = expf(-expf(a_log[h]) * seq_softplus(a[i] + dt_bias[h]));
+}
+// grid (H, ceil(dv / DR_THREADS)); thread j owns column j of the head's state S[dk][dv] for the whole call: DK > 0 keeps it in registers,
+// DK == 0 (any dk) in shared memory [dk][DR_THREADS].  Tokens run in order; per token two passes over dk:
+//   acc = sum_i S[i] k[i]           (the decayed read-out is decay * acc)
+//   u = beta * (v - decay * acc) ;  S[i] = decay * S[i] + k[i] * u ;  out = sum_i S[i] q[i]
+// k and q of the token are read at warp-uniform addresses (one broadcast transaction per load).
+#define DR_THREADS 64
+template <int DK>
+__global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                                                                const float* __restrict__ bd, float* __restrict__ state, float* __restrict__ o, int T, int H, int G,
+                                                                int dk, int dv) {
+    extern __shared__ float dr_sm[];
+    const int h = blockIdx.x, g = h / (H / G);
+    const int j = blockIdx.y * DR_THREADS + threadIdx.x;
+    const bool live = j < dv;
+    const int jj = live ? j : dv - 1;                       // idle threads shadow the last column and never store
+    float S[DK > 0 ? DK : 1];
+    float* Ss = dr_sm + threadIdx.x;                         // generic: S[i] at Ss[i * DR_THREADS]
+    float* sp = state + ((int64_t)h * dk) * dv + jj;
+    if (DK > 0) {
+#pragma unroll
+        for (int i = 0; i < DK; i++) S[i] = sp[(int64_t)i * dv];
+    } else {
+        for (int i = 0; i < dk; i++) Ss[i * DR_THREADS] = sp[(int64_t)i * dv];
+    }
+    for (int t = 0; t < T; t++) {
+        const float* kt = k + ((int64_t)t * G + g) * dk;
+        const float* qt = q + ((int64_t)t * G + g) * dk;
+        const float beta = bd[((int64_t)t * H + h) * 2], dec = bd[((int64_t)t * H + h) * 2 + 1];
+        const float vj = v[((int64_t)t * H + h) * dv + jj];
+        float acc = 0.0f, out = 0.0f;
+        if (DK > 0) {
+#pragma unroll
+            for (int i = 0; i < DK; i++) acc = fmaf(S[i], kt[i], acc);
+            const float u = beta * (vj - dec * acc);
+#pragma unroll
+            for (int i = 0; i < DK; i++) { S[i] = fmaf(kt[i], u, dec * S[i]); out = fmaf(S[i], qt[i], out); }
+        } else {
+            for (int i = 0; i < dk; i++) acc = fmaf(Ss[i * DR_THREADS], kt[i], acc);
+            const float u = beta * (vj - dec * acc);
+            for (int i = 0; i < dk; i++) { const float s = fmaf(kt[i], u, dec * Ss[i * DR_THREADS]); Ss[i * DR_THREADS] = s; out = fmaf(s, qt[i], out); }
+        }
+        if (live) o[((int64_t)t * H + h) * dv + j] = out;
+    }
+    if (live) {
+        if (DK > 0) {
+#pragma unroll
+            for (int i = 0; i < DK; i++) sp[(int64_t)i * dv] = S[i];
+        } else {
+            for (int i = 0; i < dk; i++) sp[(int64_t)i * dv] = Ss[i * DR_THREADS];
+        }
+    }
+}
+extern "C" CC_API int cc_gated_delta_rule(cc_device* dev, const cc_view* q, const cc_view* k, const cc_view* v, const cc_view* a, const cc_view* b,
+                                          const cc_view* a_log, const cc_view* dt_bias, const cc_view* state, int32_t H, int32_t G, int32_t dk, int32_t dv,
+                                          cc_buf** out) {
+    SEQ_ENTER(dev, "gated_delta_rule");
+    if (!out) return cc_fail(dev, CC_ERR_ARG, "gated_delta_rule: out is NULL");
+    SEQ_F32(dev, q, "gated_delta_rule q"); SEQ_F32(dev, k, "gated_delta_rule k"); SEQ_F32(dev, v, "gated_delta_rule v");
+    SEQ_F32(dev, a, "gated_delta_rule a"); SEQ_F32(dev, b, "gated_delta_rule b"); SEQ_F32(dev, a_log, "gated_delta_rule a_log");
+    SEQ_F32(dev, dt_bias, "gated_delta_rule dt_bias"); SEQ_F32(dev, state, "gated_delta_rule state");
+    CC_REQUIRE(dev, H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0, "gated_delta_rule: bad head counts / sizes");
+    CC_REQUIRE(dev, q->ndim == 2, "gated_delta_rule: q must be [T, n_kv * dk]");
+    const int64_t T = q->shape[0];
+    CC_REQUIRE(dev, view_len(q) == T * G * dk && view_len(k) == T * G * dk && view_len(v) == T * H * dv && view_len(a) == T * H && view_len(b) == T * H &&
+                        view_len(a_log) == H && view_len(dt_bias) == H && view_len(state) == (int64_t)H * dk * dv,
+               "gated_delta_rule: operand sizes do not fit T=%lld heads=%d kv=%d dk=%d dv=%d", (long long)T, H, G, dk, dv);
+    cc_buf* o = nullptr;
+    int rc = cc_new_activation(dev, T * H * dv, CC_F32, false, &o);
+    if (rc) return rc;
+    *out = o;
+    if (T == 0) return CC_OK;
+    void* bdp = nullptr; size_t cls = 0;
+    rc = cc_pool_alloc(dev, (size_t)T * H * 2 * 4, &bdp, &cls);
+    if (rc) return rc;
+    delta_gates_kernel<<<(unsigned)((T * H + 255) / 256), 256, 0, dev->stream>>>(fptr(a), fptr(b), fptr(a_log), fptr(dt_bias), (float*)bdp, T * H, H);
+    dev->launches++;
+    dim3 grid((unsigned)H, (unsigned)((dv + DR_THREADS - 1) / DR_THREADS));
+#define DR_ARGS fptr(q), fptr(k), fptr(v), (const float*)bdp, fptr(state), (float*)o->base, (int)T, H, G, dk, dv
+    if (dk == 32) delta_rule_kernel<32><<<grid, DR_THREADS, 0, dev->stream>>>(DR_ARGS);
+    else if (dk == 64) delta_rule_kernel<64><<<grid, DR_THREADS, 0, dev->stream>>>(DR_ARGS);
+    else if (dk == 128) delta_rule_kernel<128><<<grid, DR_THREADS, 0, dev->stream>>>(DR_ARGS);
+    else {
+        const size_t smem = (size_t)dk * DR_THREADS * 4;
+        if (smem > 200 * 1024) { cc_pool_free(dev, bdp, cls); return cc_fail(dev, CC_ERR_UNSUPPORTED, "gated_delta_rule: dk=%d is too large", dk); }
+        if (smem > 48 * 1024) CC_CUDA(dev, cudaFuncSetAttribute(delta_rule_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        delta_rule_kernel<0><<<grid, DR_THREADS, smem, dev->stream>>>(DR_ARGS);
+    }
+#undef DR_ARGS
+    cc_pool_free(dev, bdp, cls);            // stream-ordered pool: the next user of this block runs after the kernels above
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}
+
+// ---- sliding-window attention over a ring cache ---------------------------------------------------------------------------------------
+// one warp per (token, kv head)
+__global__ void kv_ring_append_kernel(float* __restrict__ kring, float* __restrict__ vring, const float* __restrict__ k, const float* __restrict__ v,
+                                      const float* __restrict__ knw, float eps, int64_t pos0, int ring, int T, int G, int dk, int dv) {
+    const int64_t u = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (u >= (int64_t)T * G) return;
+    const int t = (int)(u / G), g = (int)(u % G);
+    const int64_t row = (pos0 + t) % ring;
+    const float* kr = k + ((int64_t)t * G + g) * dk;
+    float* kd = kring + (row * G + g) * dk;
+    if (knw) {
+        float ss = 0.0f;
+        for (int c = lane; c < dk; c += 32) ss = fmaf(kr[c], kr[c], ss);
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)dk + eps);
+        for (int c = lane; c < dk; c += 32) kd[c] = kr[c] * inv * knw[c];
+    } else {
+        for (int c = lane; c < dk; c += 32) kd[c] = kr[c];
+    }
+    const float* vr = v + ((int64_t)t * G + g) * dv;
+    float* vd = vring + (row * G + g) * dv;
+    for (int c = lane; c < dv; c += 32) vd[c] = vr[c];
+}
+extern "C" CC_API int cc_kv_ring_append(cc_device* dev, const cc_view* kring, const cc_view* vring, const cc_view* k, const cc_view* v, const cc_view* knw,
+                                        float eps, int64_t pos0, int32_t G, int32_t dk, int32_t dv) {
+    SEQ_ENTER(dev, "kv_ring_append");
+    SEQ_F32(dev, kring, "kv_ring_append kring"); SEQ_F32(dev, vring, "kv_ring_append vring"); SEQ_F32(dev, k, "kv_ring_append k"); SEQ_F32(dev, v, "kv_ring_append v");
+    if (knw) { SEQ_F32(dev, knw, "kv_ring_append k_norm_w"); CC_REQUIRE(dev, view_len(knw) == dk, "kv_ring_append: k_norm_w must have dk elements"); }
+    CC_REQUIRE(dev, G > 0 && dk > 0 && dv > 0 && kring->ndim == 2 && k->ndim == 2 && pos0 >= 0, "kv_ring_append: bad arguments");
+    const int64_t ring = kring->shape[0], T = k->shape[0];
+    CC_REQUIRE(dev, view_len(kring) == ring * G * dk && view_len(vring) == ring * G * dv && view_len(k) == T * G * dk && view_len(v) == T * G * dv,
+               "kv_ring_append: operand sizes do not fit kv=%d dk=%d dv=%d", G, dk, dv);
+    CC_REQUIRE(dev, T <= ring, "kv_ring_append: %lld tokens do not fit a ring of %lld", (long long)T, (long long)ring);
+    if (T == 0) return CC_OK;
+    kv_ring_append_kernel<<<(unsigned)((T * G + 7) / 8), 256, 0, dev->stream>>>(fptr(kring), fptr(vring), fptr(k), fptr(v), knw ? fptr(knw) : nullptr, eps, pos0, (int)ring,
+                                                                             (int)T, G, dk, dv);
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}
+
+// grid (T, H), WA_THREADS threads.  Shared memory: q[dk] then one score per visible key.  Keys are dealt to warps round-robin; a warp's
+// lanes stride the head dimension and butterfly-reduce each dot product; the value sum of output column d runs over the keys in
+// ascending position.  The result for a query depends only on (query, visible keys), not on T.
+#define WA_THREADS 128
+__global__ void __launch_bounds__(WA_THREADS) window_attention_kernel(const float* __restrict__ q, const float* __restrict__ qnw, float eps, const float* __restrict__ kring,
+                                                                      const float* __restrict__ vring, float* __restrict__ out, int64_t pos0, int ring, int H, int G, int dk,
+                                                                      int dv, int window, float scale, const float* __restrict__ r1, const float* __restrict__ r2) {
+    extern __shared__ float wa_sm[];
+    __shared__ float red[WA_THREADS / 32];
+    float* sq = wa_sm;
+    float* sc = wa_sm + ((dk + 3) & ~3);
+    const int t = blockIdx.x, h = blockIdx.y, g = h / (H / G);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t i = pos0 + t;
+    const int64_t lo = (window > 0 && i - window + 1 > 0) ? i - window + 1 : 0;
+    const int n = (int)(i - lo + 1);
+    // query head -> shared memory, RMS-normalised
+    const float* qr = q + ((int64_t)t * H + h) * dk;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < dk; c += WA_THREADS) { const float x = qr[c]; sq[c] = x; ss = fmaf(x, x, ss); }
+    if (qnw) {
+        ss = warp_sum(ss);
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        float tot = 0.0f;
+        for (int w = 0; w < WA_THREADS / 32; w++) tot += red[w];
+        const float inv = 1.0f / sqrtf(tot / (float)dk + eps);
+        for (int c = threadIdx.x; c < dk; c += WA_THREADS) sq[c] = sq[c] * inv * qnw[c];
+        __syncthreads();
+    } else __syncthreads();
+    const float hr1 = r1 ? r1[h] : 0.0f, hr2 = r2 ? r2[h] : 0.0f;
+    float mx = -INFINITY;
+    for (int jj = warp; jj < n; jj += WA_THREADS / 32) {
+        const int64_t p = lo + jj;
+        const float* kr = kring + ((p % ring) * G + g) * dk;
+        float d = 0.0f;
+        for (int c = lane; c < dk; c += 32) d = fmaf(sq[c], kr[c], d);
+        d = warp_sum(d);
+        float s = d * scale;
+        if (r1) s -= hr1 * log1pf(hr2 * (float)(i - p));
+        if (lane == 0) sc[jj] = s;
+        mx = fmaxf(mx, s);
+    }
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    mx = red[0];
+    for (int w = 1; w < WA_THREADS / 32; w++) mx = fmaxf(mx, red[w]);
+    __syncthreads();
+    float sum = 0.0f;
+    for (int jj = threadIdx.x; jj < n; jj += WA_THREADS) { const float e = expf(sc[jj] - mx); sc[jj] = e; sum += e; }
+    sum = warp_sum(sum);
+    if (lane == 0) red[warp] = sum;
+    __syncthreads();
+    float tot = 0.0f;
+    for (int w = 0; w < WA_THREADS / 32; w++) tot += red[w];
+    const float inv = 1.0f / tot;
+    for (int d = threadIdx.x; d < dv; d += WA_THREADS) {
+        float acc = 0.0f;
+        for (int jj = 0; jj < n; jj++) acc = fmaf(sc[jj], vring[(((lo + jj) % ring) * G + g) * dv + d], acc);
+        out[((int64_t)t * H + h) * dv + d] = acc * inv;
+    }
+}
+extern "C" CC_API int cc_window_attention(cc_device* dev, const cc_view* q, const cc_view* qnw, float eps, const cc_view* kring, const cc_view* vring, int64_t pos0,
+                                          int32_t H, int32_t G, int32_t dk, int32_t dv, int32_t window, float scale, const cc_view* r1, const cc_view* r2,
+                                          cc_buf** out) {
+    SEQ_ENTER(dev, "window_attention");
+    if (!out) return cc_fail(dev, CC_ERR_ARG, "window_attention: out is NULL");
+    SEQ_F32(dev, q, "window_attention q"); SEQ_F32(dev, kring, "window_attention kring"); SEQ_F32(dev, vring, "window_attention vring");
+    if (qnw) { SEQ_F32(dev, qnw, "window_attention q_norm_w"); CC_REQUIRE(dev, view_len(qnw) == dk, "window_attention: q_norm_w must have dk elements"); }
+    CC_REQUIRE(dev, (r1 == nullptr) == (r2 == nullptr), "window_attention: r1 and r2 come together");
+    if (r1) {
+        SEQ_F32(dev, r1, "window_attention r1"); SEQ_F32(dev, r2, "window_attention r2");
+        CC_REQUIRE(dev, view_len(r1) == H && view_len(r2) == H, "window_attention: r1 / r2 must have one number per head");
+    }
+    CC_REQUIRE(dev, H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0 && q->ndim == 2 && kring->ndim == 2 && pos0 >= 0, "window_attention: bad arguments");
+    const int64_t T = q->shape[0], ring = kring->shape[0];
+    CC_REQUIRE(dev, view_len(q) == T * H * dk && view_len(kring) == ring * G * dk && view_len(vring) == ring * G * dv,
+               "window_attention: operand sizes do not fit heads=%d kv=%d dk=%d dv=%d", H, G, dk, dv);
+    // the oldest row the first query needs must not have been overwritten by the newest row of this call
+    const int64_t last = pos0 + T - 1;
+    const int64_t oldest = window > 0 ? (pos0 - window + 1 > 0 ? pos0 - window + 1 : 0) : 0;
+    CC_REQUIRE(dev, T == 0 || last - oldest + 1 <= ring, "window_attention: positions %lld..%lld with window %d need more than the ring's %lld rows",
+               (long long)pos0, (long long)last, window, (long long)ring);
+    cc_buf* o = nullptr;
+    int rc = cc_new_activation(dev, T * H * dv, CC_F32, false, &o);
+    if (rc) return rc;
+    *out = o;
+    if (T == 0) return CC_OK;
+    const int64_t maxn = window > 0 ? (window < last + 1 ? window : last + 1) : last + 1;
+    const size_t smem = ((size_t)((dk + 3) & ~3) + (size_t)maxn) * 4;
+    if (smem > 200 * 1024) return cc_fail(dev, CC_ERR_UNSUPPORTED, "window_attention: %lld visible keys need %zu bytes of shared memory", (long long)maxn, smem);
+    if (smem > 48 * 1024) CC_CUDA(dev, cudaFuncSetAttribute(window_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid((unsigned)T, (unsigned)H);
+    window_attention_kernel<<<grid, WA_THREADS, smem, dev->stream>>>(fptr(q), qnw ? fptr(qnw) : nullptr, eps, fptr(kring), fptr(vring), (float*)o->base, pos0, (int)ring, H, G,
+                                                                   dk, dv, window, scale, r1 ? fptr(r1) : nullptr, r2 ? fptr(r2) : nullptr);
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}

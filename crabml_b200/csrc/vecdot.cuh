@@ -3,6 +3,7 @@
 // the xor-butterfly warp_sum.  Shared by the eager kernel (matvec.cu) and the generic MATVEC phase of the megakernel (mega.cu), so
 // both produce the same bits.  T::stage_act copies the activation scratch (quantize.cu layout) into shared memory.
 #pragma once
+#include <cuda_bf16.h>
 #include "common.cuh"
 
 
@@ -434,6 +435,34 @@ struct TF32 {
         const float* a = (const float*)sm;
         float acc = 0.0f;
         for (int i = lane; i < k; i += 32) acc += w[i] * a[i];
+        return acc;
+    }
+};
+// plain bfloat16 weights: the f32 activation is rounded to bfloat16 while it is staged (kept as f32 bit patterns: a bf16 value is an
+// f32 whose low 16 bits are zero), the products are exact in f32, the accumulation is f32.  16-byte streaming loads of 8 weights.
+struct TBF16 {
+    static __host__ __device__ int smem_bytes(int k) { return al16i(k * 4); }
+    static __device__ void stage_act(const void* x, int64_t, int bi, int k, uint8_t* sm) {
+        const float* src = (const float*)x + (int64_t)bi * k;
+        float* d = (float*)sm;
+        for (int i = threadIdx.x; i < k; i += blockDim.x) d[i] = __bfloat162float(__float2bfloat16_rn(src[i]));
+    }
+    static __device__ float row_dot(const WPlanes& W, int64_t row, int k, const uint8_t* sm, int lane) {
+        const uint16_t* w = (const uint16_t*)W.p[0] + row * (int64_t)k;
+        const float* a = (const float*)sm;
+        float acc = 0.0f;
+        if ((k & 7) == 0) {
+            for (int c = lane; c < (k >> 3); c += 32) {
+                const int4 v = ld_stream_16(w + c * 8);
+                const float4 a0 = *(const float4*)(a + c * 8), a1 = *(const float4*)(a + c * 8 + 4);
+                acc = fmaf(__uint_as_float((unsigned)v.x << 16), a0.x, acc); acc = fmaf(__uint_as_float((unsigned)v.x & 0xFFFF0000u), a0.y, acc);
+                acc = fmaf(__uint_as_float((unsigned)v.y << 16), a0.z, acc); acc = fmaf(__uint_as_float((unsigned)v.y & 0xFFFF0000u), a0.w, acc);
+                acc = fmaf(__uint_as_float((unsigned)v.z << 16), a1.x, acc); acc = fmaf(__uint_as_float((unsigned)v.z & 0xFFFF0000u), a1.y, acc);
+                acc = fmaf(__uint_as_float((unsigned)v.w << 16), a1.z, acc); acc = fmaf(__uint_as_float((unsigned)v.w & 0xFFFF0000u), a1.w, acc);
+            }
+        } else {
+            for (int i = lane; i < k; i += 32) acc = fmaf(__uint_as_float((unsigned)w[i] << 16), a[i], acc);
+        }
         return acc;
     }
 };

@@ -1,0 +1,310 @@
+"""The Zatorax decoder family: configuration, weight loading and the Python handle on its C++ runner
+(crabml_b200/csrc/host/zatorax_runner.cpp).
+
+A model folder holds config.json and model.safetensors.  config.json gives every size and every constant that can differ between
+models of the family: `vocab`, `width`, `norm.eps` and `layers`, a list whose entries name the layer's mixer (`type`: "delta" or
+"attention"), the mixer's sizes (`mixer`) and its feed-forward (`mlp`, or null).  Tensor names: `embed`, `head`, `final.norm`,
+and per layer i `l<i>.norm1`, `l<i>.norm2`, `l<i>.mix.*`, `l<i>.mlp.*` (experts `e0`, `e1`, ..., `shared`, `router`, `correction`).
+
+Precision: `dtype="bfloat16"` keeps the matrices in bfloat16 (activations are rounded to bfloat16 at the input of a product, sums are
+32-bit); `dtype="float32"` widens them to f32 and every product is a true 32-bit one.  In both modes the residual stream, norms,
+softmax, routers, convolutions, gates and the recurrent state are 32-bit.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import json
+import os
+import struct
+
+import numpy as np
+
+from . import capi
+from .capi import CudaError, TensorError
+from .tensor import CudaTensor, CudaTensorDevice
+
+ARCHITECTURE = "Zatorax"
+MIXERS = {"delta": 0, "attention": 1}
+
+
+# ---- configuration ----------------------------------------------------------------------------------------------------------------
+def parse_config(conf: dict) -> dict:
+    """Validates a config.json dict and fills the optional keys, so that the rest of the code reads one shape of dict."""
+    if conf.get("architecture", ARCHITECTURE) != ARCHITECTURE:
+        raise TensorError(f"not a {ARCHITECTURE} config: architecture = {conf.get('architecture')!r}")
+    out = {"architecture": ARCHITECTURE, "vocab": int(conf["vocab"]), "width": int(conf["width"]), "norm": {"eps": float(conf["norm"]["eps"])}, "layers": []}
+    for i, L in enumerate(conf["layers"]):
+        kind = L["type"]
+        if kind not in MIXERS:
+            raise TensorError(f"layer {i}: unknown mixer type {kind!r}")
+        m = dict(L["mixer"])
+        for key in ("heads", "kv_heads", "dim", "vdim"):
+            m[key] = int(m[key])
+        if kind == "delta":
+            m["conv"] = int(m["conv"])
+        else:
+            m["mask"] = {"size": int(m["mask"]["size"])}
+            m["scale"] = float(m["scale"])
+            m["kv_from"] = None if m.get("kv_from") is None else int(m["kv_from"])
+        mlp = L.get("mlp")
+        if mlp is not None:
+            if mlp.get("kind", "moe") != "moe":
+                raise TensorError(f"layer {i}: unknown feed-forward kind {mlp.get('kind')!r}")
+            r = mlp["router"]
+            g = r.get("groups") or {"count": 1, "keep": 1}
+            mlp = {"kind": "moe", "expert": {"ff": int(mlp["expert"]["ff"])},
+                   "router": {"experts": int(r["experts"]), "top": int(r["top"]), "groups": {"count": int(g["count"]), "keep": int(g["keep"])}},
+                   "shared": {"ff": int(mlp["shared"]["ff"])} if mlp.get("shared") else None}
+        out["layers"].append({"type": kind, "mixer": m, "mlp": mlp})
+    return out
+
+
+def expected_tensors(conf: dict) -> dict:
+    """name -> shape of every tensor a model of this config has."""
+    D, V = conf["width"], conf["vocab"]
+    t = {"embed": [V, D], "head": [V, D], "final.norm": []}
+    for i, L in enumerate(conf["layers"]):
+        m, p = L["mixer"], f"l{i}."
+        H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        t[p + "norm1"] = []
+        if L["type"] == "delta":
+            K = m["conv"]
+            t.update({p + "mix.q": [G * dk, D], p + "mix.q.conv": [G * dk, K], p + "mix.k": [G * dk, D], p + "mix.k.conv": [G * dk, K],
+                      p + "mix.v": [H * dv, D], p + "mix.v.conv": [H * dv, K], p + "mix.b": [H, D], p + "mix.A_log": [H], p + "mix.norm": [dv],
+                      p + "mix.a": [H, D], p + "mix.dt_bias": [H], p + "mix.g": [H * dv, D], p + "mix.o": [D, H * dv]})
+        else:
+            t.update({p + "mix.q": [H * dk, D], p + "mix.q.norm": [dk], p + "mix.r1": [H], p + "mix.r2": [H], p + "mix.o": [D, H * dv]})
+            if m.get("kv_from") is None:
+                t.update({p + "mix.k": [G * dk, D], p + "mix.v": [G * dv, D], p + "mix.k.norm": [dk]})
+        mlp = L["mlp"]
+        if mlp:
+            t[p + "norm2"] = []
+            E, ff = mlp["router"]["experts"], mlp["expert"]["ff"]
+            t[p + "mlp.router"] = [E, D]
+            t[p + "mlp.correction"] = [E]
+            names = [f"e{e}" for e in range(E)]
+            for n in names:
+                t.update({f"{p}mlp.{n}.gate": [ff, D], f"{p}mlp.{n}.up": [ff, D], f"{p}mlp.{n}.down": [D, ff]})
+            if mlp["shared"]:
+                sf = mlp["shared"]["ff"]
+                t.update({p + "mlp.shared.gate": [sf, D], p + "mlp.shared.up": [sf, D], p + "mlp.shared.down": [D, sf]})
+    return t
+
+
+# ---- safetensors: 8-byte little-endian header length, JSON header (name -> dtype, shape, data_offsets), then the data ---------------
+def bf16_to_f32(u16: np.ndarray) -> np.ndarray:
+    return (u16.astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16(x: np.ndarray) -> np.ndarray:
+    """round to nearest even, as uint16 bit patterns"""
+    u = np.ascontiguousarray(x, np.float32).view(np.uint32)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def read_safetensors(path: str) -> dict:
+    """-> ({name: ndarray}, names stored as bfloat16); bfloat16 tensors come back as their uint16 bit patterns."""
+    with open(path, "rb") as f:
+        (n,) = struct.unpack("<Q", f.read(8))
+        meta = json.loads(f.read(n))
+        data = f.read()
+    kinds = {"BF16": np.uint16, "F32": np.float32, "F16": np.float16, "I32": np.int32}
+    out, bf16 = {}, set()
+    for name, m in meta.items():
+        if name == "__metadata__":
+            continue
+        if m["dtype"] not in kinds:
+            raise TensorError(f"{name}: unsupported dtype {m['dtype']}")
+        a, b = m["data_offsets"]
+        out[name] = np.frombuffer(data[a:b], kinds[m["dtype"]]).reshape(m["shape"])
+        if m["dtype"] == "BF16":
+            bf16.add(name)
+    return out, bf16
+
+
+def write_safetensors(path: str, tensors: dict):
+    """tensors: {name: float32 ndarray}; stored as bfloat16 (used by tests and examples to make model folders)."""
+    meta, blobs, off = {}, [], 0
+    for name, a in tensors.items():
+        raw = f32_to_bf16(np.asarray(a, np.float32)).tobytes()
+        meta[name] = {"dtype": "BF16", "shape": list(np.asarray(a).shape), "data_offsets": [off, off + len(raw)]}
+        blobs.append(raw)
+        off += len(raw)
+    hdr = json.dumps(meta).encode()
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(hdr)) + hdr + b"".join(blobs))
+
+
+def random_weights(conf: dict, seed: int = 0, scale: float = 1.0) -> dict:
+    """Random weights of a config (float32 arrays whose values are exact in bfloat16), sized so that activations stay O(1)."""
+    rng = np.random.default_rng(seed)
+    out = {}
+    for name, shape in expected_tensors(conf).items():
+        leaf = name.split(".")[-1]
+        if name.endswith("norm1") or name.endswith("norm2") or name == "final.norm":
+            a = np.asarray(1.0 + 0.1 * rng.standard_normal(), np.float32)
+        elif leaf == "norm":                                       # per-head norm weights
+            a = 1.0 + 0.1 * rng.standard_normal(shape)
+        elif leaf == "conv":
+            a = rng.standard_normal(shape) * 0.5
+        elif leaf == "A_log":
+            a = np.log(rng.uniform(0.5, 4.0, shape))
+        elif leaf == "dt_bias":
+            a = rng.uniform(-3.0, 0.0, shape)
+        elif leaf == "r1":
+            a = rng.uniform(0.2, 1.5, shape)
+        elif leaf == "r2":
+            a = rng.uniform(0.05, 1.0, shape)
+        elif leaf == "correction":
+            a = rng.standard_normal(shape) * 0.05
+        elif name == "embed":
+            a = rng.standard_normal(shape)
+        else:
+            a = rng.standard_normal(shape) * (scale / np.sqrt(shape[-1]))
+        out[name] = bf16_to_f32(f32_to_bf16(np.asarray(a, np.float32))).reshape(shape)
+    return out
+
+
+# ---- the model on a device ------------------------------------------------------------------------------------------------------------
+class ZatoraxModel:
+    """Weights of one model on one device + its runner.  `weights`: {name: float32 ndarray} (values representable in bfloat16 when
+    dtype == "bfloat16") or the pair read_safetensors returns."""
+
+    def __init__(self, device: CudaTensorDevice, conf: dict, weights, dtype: str = "bfloat16", chunk: int = 0):
+        if dtype not in ("bfloat16", "float32"):
+            raise TensorError(f"dtype must be bfloat16 or float32, not {dtype!r}")
+        self.device, self.conf, self.dtype = device, parse_config(conf), dtype
+        bf16_names = set()
+        if isinstance(weights, tuple):
+            weights, bf16_names = weights
+        want = expected_tensors(self.conf)
+        missing = [n for n in want if n not in weights]
+        if missing:
+            raise TensorError(f"model is missing {len(missing)} tensors, first: {missing[0]}")
+        for n, shape in want.items():
+            if list(np.asarray(weights[n]).shape) != list(shape):
+                raise TensorError(f"tensor {n}: shape {list(np.asarray(weights[n]).shape)} in the file, {list(shape)} by the config")
+
+        def f32(name):
+            a = weights[name]
+            return bf16_to_f32(a) if name in bf16_names else np.asarray(a, np.float32)
+
+        def vec(name):                                                     # small parameters: always f32 on the device
+            a = np.ascontiguousarray(f32(name), np.float32).reshape(-1)
+            return CudaTensor.from_cpu(a, [a.size], capi.F32, device)
+
+        def mat_from(a32, bits16):                                         # a product's matrix: bf16 or f32 by the mode
+            shape = list(a32.shape if a32 is not None else bits16.shape)
+            if dtype == "float32":
+                return CudaTensor.from_cpu(np.ascontiguousarray(a32 if a32 is not None else bf16_to_f32(bits16), np.float32), shape, capi.F32, device)
+            return CudaTensor.from_cpu(np.ascontiguousarray(bits16 if bits16 is not None else f32_to_bf16(a32)), shape, capi.BF16, device)
+
+        def mat(name):
+            a = weights[name]
+            return mat_from(None, np.asarray(a)) if name in bf16_names else mat_from(np.asarray(a, np.float32), None)
+
+        def stack(names):
+            arrs = [weights[n] for n in names]
+            if all(n in bf16_names for n in names):
+                return mat_from(None, np.concatenate([np.asarray(a) for a in arrs], 0))
+            return mat_from(np.concatenate([f32(n) for n in names], 0), None)
+
+        c = self.conf
+        self.tensors = {"embed": CudaTensor.from_cpu(np.ascontiguousarray(f32("embed")), [c["vocab"], c["width"]], capi.F32, device),
+                        "final.norm": vec("final.norm"), "head": mat("head")}
+        lcs = (capi.czr_layer_config * len(c["layers"]))()
+        lws = (capi.czr_layer_weights * len(c["layers"]))()
+        for i, L in enumerate(c["layers"]):
+            m, mlp, p = L["mixer"], L["mlp"], f"l{i}."
+            lc = lcs[i]
+            lc.mixer, lc.heads, lc.kv_heads, lc.dim, lc.vdim = MIXERS[L["type"]], m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            lc.conv, lc.window, lc.kv_from, lc.scale = 0, 0, -1, 0.0
+            t = {"norm1": vec(p + "norm1")}
+            if L["type"] == "delta":
+                lc.conv = m["conv"]
+                for k in ("q", "k", "v", "b", "a", "g", "o"):
+                    t[k] = mat(p + "mix." + k)
+                for k in ("q", "k", "v"):
+                    t[k + "_conv"] = CudaTensor.from_cpu(np.ascontiguousarray(f32(f"{p}mix.{k}.conv")), list(weights[f"{p}mix.{k}.conv"].shape), capi.F32, device)
+                t["a_log"], t["dt_bias"], t["out_norm"] = vec(p + "mix.A_log"), vec(p + "mix.dt_bias"), vec(p + "mix.norm")
+            else:
+                lc.window, lc.scale = m["mask"]["size"], m["scale"]
+                lc.kv_from = -1 if m.get("kv_from") is None else m["kv_from"]
+                t["q"], t["o"] = mat(p + "mix.q"), mat(p + "mix.o")
+                t["q_norm"], t["r1"], t["r2"] = vec(p + "mix.q.norm"), vec(p + "mix.r1"), vec(p + "mix.r2")
+                if lc.kv_from < 0:
+                    t["k"], t["v"], t["k_norm"] = mat(p + "mix.k"), mat(p + "mix.v"), vec(p + "mix.k.norm")
+            lc.has_mlp = int(mlp is not None)
+            if mlp:
+                r = mlp["router"]
+                lc.experts, lc.top, lc.groups, lc.keep_groups, lc.expert_ff = r["experts"], r["top"], r["groups"]["count"], r["groups"]["keep"], mlp["expert"]["ff"]
+                lc.shared_ff = mlp["shared"]["ff"] if mlp["shared"] else 0
+                t["norm2"] = vec(p + "norm2")
+                t["router"] = CudaTensor.from_cpu(np.ascontiguousarray(f32(p + "mlp.router")), [r["experts"], c["width"]], capi.F32, device)
+                t["correction"] = vec(p + "mlp.correction")
+                for part, key in (("gate", "e_gate"), ("up", "e_up"), ("down", "e_down")):
+                    t[key] = stack([f"{p}mlp.e{e}.{part}" for e in range(r["experts"])])
+                if mlp["shared"]:
+                    for part in ("gate", "up", "down"):
+                        t["s_" + part] = mat(f"{p}mlp.shared.{part}")
+            for k, v in t.items():
+                setattr(lws[i], k, v.buf.handle.value if hasattr(v.buf.handle, 'value') else v.buf.handle)
+                self.tensors[f"{p}{k}"] = v                                  # keep alive
+        cc = capi.czr_config(len(c["layers"]), c["width"], c["vocab"], c["norm"]["eps"], int(chunk))
+        h = C.c_void_p()
+        rc = device.lib.czr_runner_create(device.handle, C.byref(cc), lcs, lws, self.tensors["embed"].buf.handle, self.tensors["final.norm"].buf.handle,
+                                          self.tensors["head"].buf.handle, C.byref(h))
+        if rc != capi.CC_OK:
+            raise (TensorError if rc == capi.CC_ERR_TENSOR else CudaError)(f"czr_runner_create failed [{rc}]: {device.lib.czr_last_create_error().decode()}")
+        self.handle = h
+        self._keep = (lcs, lws)
+
+    # ---- sequences -----------------------------------------------------------------------------------------------------------------
+    def _check(self, rc):
+        if rc == capi.CC_OK:
+            return
+        msg = self.device.lib.czr_runner_last_error(self.handle).decode()
+        raise (TensorError if rc == capi.CC_ERR_TENSOR else CudaError)(msg)
+
+    def open(self) -> int:
+        s = C.c_int32(-1)
+        self._check(self.device.lib.czr_seq_open(self.handle, C.byref(s)))
+        return int(s.value)
+
+    def close_seq(self, slot: int):
+        self._check(self.device.lib.czr_seq_close(self.handle, int(slot)))
+
+    def seq_len(self, slot: int) -> int:
+        return int(self.device.lib.czr_seq_len(self.handle, int(slot)))
+
+    def stats(self) -> dict:
+        a = (C.c_int64 * 3)()
+        self._check(self.device.lib.czr_runner_stats(self.handle, a))
+        return {"slots": int(a[0]), "live": int(a[1]), "state_bytes_per_slot": int(a[2])}
+
+    def step(self, slot: int, tokens, want=()) -> np.ndarray:
+        """feeds the sequence's next tokens; -> logits [len(want), vocab] of the wanted places among them"""
+        toks = (C.c_int64 * len(tokens))(*[int(t) for t in tokens])
+        w = (C.c_int32 * max(1, len(want)))(*[int(i) for i in want])
+        out = np.zeros((len(want), self.conf["vocab"]), np.float32)
+        self._check(self.device.lib.czr_runner_step(self.handle, int(slot), toks, len(tokens), w, len(want), out.ctypes.data_as(C.c_void_p) if len(want) else None))
+        return out
+
+    def generate_greedy(self, slot: int, prompt, steps: int, eos: int = -1):
+        p = (C.c_int64 * len(prompt))(*[int(t) for t in prompt])
+        out = (C.c_int64 * max(1, steps))()
+        n = C.c_int32(0)
+        self._check(self.device.lib.czr_runner_generate_greedy(self.handle, int(slot), p, len(prompt), steps, eos, out, C.byref(n)))
+        return [int(out[i]) for i in range(n.value)]
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.device.lib.czr_runner_destroy(self.handle)
+            self.handle = None
+
+
+def load(path: str, device: CudaTensorDevice, dtype: str = "bfloat16", chunk: int = 0) -> ZatoraxModel:
+    """path: a folder with config.json and model.safetensors"""
+    with open(os.path.join(path, "config.json")) as f:
+        conf = json.load(f)
+    return ZatoraxModel(device, conf, read_safetensors(os.path.join(path, "model.safetensors")), dtype, chunk)

@@ -47,7 +47,9 @@ extern "C" {
 enum cc_ggml_type {
     CC_F32 = 0, CC_F16 = 1, CC_Q4_0 = 2, CC_Q4_1 = 3, CC_Q5_0 = 6, CC_Q5_1 = 7,
     CC_Q8_0 = 8, CC_Q8_1 = 9, CC_Q2_K = 10, CC_Q3_K = 11, CC_Q4_K = 12,
-    CC_Q5_K = 13, CC_Q6_K = 14, CC_Q8_K = 15
+    CC_Q5_K = 13, CC_Q6_K = 14, CC_Q8_K = 15,
+    CC_I32 = 26,    /* index tensors (routing tables); never an operand of arithmetic */
+    CC_BF16 = 30    /* plain bfloat16 weights: matmul_vec rounds the activation to bfloat16 and accumulates in 32 bits */
 };
 
 /* RopeMode, api.rs:5-9 */

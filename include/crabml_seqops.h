@@ -1,0 +1,87 @@
+/*
+ * crabml_seqops.h -- sequence-mixing, routing and normalisation ops beyond the reference's `Tensor` trait.
+ *
+ * The reference's trait (crabml-core/src/tensor/api.rs:11-79) covers the llama family: rope, softmax attention over a growing
+ * cache, a dense gated feed-forward.  The ops below are the building blocks of hybrid decoders (recurrent and windowed mixers,
+ * routed feed-forwards, norms on the sublayer output).  Every constant of a mechanism is a parameter, so that any model built
+ * from these mechanisms can use them; crabml_b200/csrc/host/zatorax_runner.cpp is the first user.
+ *
+ * Conventions are those of crabml_cuda.h: cc_view = buffer + shape + strides (contiguous views only here), all work on the
+ * device's stream, status codes, nothing blocks.  Activations and all state are F32; everything a recurrence, a norm, a softmax
+ * or a router computes is computed in 32-bit floats.  Weight matrices of the dense products may be F32 or BF16 (cc_matmul_vec:
+ * BF16 weights round the activation to bfloat16 and accumulate in 32 bits).  These ops are eager-only: a lazy (graph /
+ * megakernel) device refuses them with CC_ERR_UNSUPPORTED.
+ */
+#ifndef CRABML_SEQOPS_H
+#define CRABML_SEQOPS_H
+
+#include "crabml_cuda.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum cc_activation { CC_ACT_NONE = 0, CC_ACT_SILU = 1, CC_ACT_GELU_TANH = 2 };
+
+/* x (any shape) = 0 */
+CC_API int cc_tensor_zero(cc_device* dev, const cc_view* x);
+
+/* ---- norms ------------------------------------------------------------------------------------------------------------------ */
+/* dst[r] = (accumulate ? dst[r] : 0) + y[r] / sqrt(mean(y[r]^2) + eps) * gain ; dst, y: [rows, cols]; gain: 1 element (one number
+ * for all coordinates) or cols elements.  accumulate = 1 is the residual update of a block whose norm sits on the sublayer OUTPUT. */
+CC_API int cc_rms_norm_gain(cc_device* dev, const cc_view* dst, const cc_view* y, const cc_view* gain, float eps, int32_t accumulate);
+/* x[r, h, :] = x[r, h, :] / sqrt(mean(x[r, h, :]^2) + eps) * w[:] * act(gate[r, h, :]) ; x, gate: [rows, heads * head_size], w: [head_size] */
+CC_API int cc_gated_head_rms_norm(cc_device* dev, const cc_view* x, const cc_view* gate, const cc_view* w, int32_t head_size, float eps,
+                                  int32_t gate_act);
+/* gate = act(gate) * up, elementwise (the inner step of a gated feed-forward, exact 32-bit activation) */
+CC_API int cc_glu_inplace(cc_device* dev, const cc_view* gate, const cc_view* up, int32_t act);
+
+/* ---- short causal convolution over time (depthwise) --------------------------------------------------------------------------- */
+/* x: [T, C] the new inputs of one sequence; w: [C, K] (the last column multiplies the current input); tail: [K-1, C], the K-1 inputs
+ * that precede x (zeros at the start of a sequence) -- read, then replaced by the last K-1 inputs of tail ++ x.
+ * out[t, c] = act(sum_j w[c, j] * in[t - (K-1) + j, c]).  unit_norm != 0: afterwards every run of head_size channels is divided by
+ * sqrt(sum of its squares + unit_eps) and multiplied by unit_scale. */
+CC_API int cc_short_conv(cc_device* dev, const cc_view* x, const cc_view* w, const cc_view* tail, int32_t act, int32_t head_size,
+                         int32_t unit_norm, float unit_eps, float unit_scale, cc_buf** out);
+
+/* ---- gated delta rule ------------------------------------------------------------------------------------------------------ */
+/* One sequence, T new tokens.  q, k: [T, n_kv * dk] (already normalised), v: [T, n_heads * dv]; a, b: [T, n_heads] raw projections;
+ * a_log, dt_bias: [n_heads]; state: [n_heads, dk, dv] F32, carried between calls.  Head h reads q/k head h / (n_heads / n_kv).
+ *   beta = sigmoid(b) ; decay = exp(-exp(a_log) * softplus(a + dt_bias))
+ *   S = decay * S ; u = beta * (v - S^T k) ; S = S + k u^T ; out = S^T q      (in this order, per token)
+ * out: [T, n_heads * dv]. */
+CC_API int cc_gated_delta_rule(cc_device* dev, const cc_view* q, const cc_view* k, const cc_view* v, const cc_view* a, const cc_view* b,
+                               const cc_view* a_log, const cc_view* dt_bias, const cc_view* state, int32_t n_heads, int32_t n_kv, int32_t dk,
+                               int32_t dv, cc_buf** out);
+
+/* ---- sliding-window attention over a ring cache ------------------------------------------------------------------------------ */
+/* Append T tokens at positions pos0 .. pos0+T-1 to a ring of `ring` positions (position p lives in row p % ring):
+ * kring: [ring, n_kv * dk], vring: [ring, n_kv * dv]; k: [T, n_kv * dk], v: [T, n_kv * dv].  k_norm_w ([dk], may be NULL): each key
+ * head is RMS-normalised (eps) and multiplied by it before it is stored. */
+CC_API int cc_kv_ring_append(cc_device* dev, const cc_view* kring, const cc_view* vring, const cc_view* k, const cc_view* v,
+                             const cc_view* k_norm_w, float eps, int64_t pos0, int32_t n_kv, int32_t dk, int32_t dv);
+/* q: [T, n_heads * dk] raw queries of positions pos0 .. ; q_norm_w ([dk], may be NULL): per-head RMS norm (eps) times weight.
+ * Position i attends to j with 0 <= i - j < window (window <= 0: no limit but j >= 0); the ring must still hold those rows.
+ *   score = (q . k) * scale - r1[h] * ln(1 + r2[h] * (i - j))        (r1, r2: [n_heads], both NULL = no distance term)
+ * then softmax over the visible keys and the weighted sum of values.  out: [T, n_heads * dv]. */
+CC_API int cc_window_attention(cc_device* dev, const cc_view* q, const cc_view* q_norm_w, float eps, const cc_view* kring, const cc_view* vring,
+                               int64_t pos0, int32_t n_heads, int32_t n_kv, int32_t dk, int32_t dv, int32_t window, float scale,
+                               const cc_view* r1, const cc_view* r2, cc_buf** out);
+
+/* ---- routed feed-forward ---------------------------------------------------------------------------------------------------- */
+/* x: [T, D]; router_w: [E, D] F32; correction: [E] or NULL.  s = softmax(router_w x) over all experts (32-bit).  Choice score =
+ * s + correction.  Experts form n_groups equal groups of neighbours; a group's score is its largest choice score; only experts of the
+ * keep_groups best groups can be chosen (n_groups <= 1: no limit).  The `top` experts with the largest choice scores are chosen; their
+ * weights are s (without the correction), not renormalised unless renormalise != 0.
+ * ids_out: I32 [T, top]; weights_out: F32 [T, top]. */
+CC_API int cc_moe_route(cc_device* dev, const cc_view* x, const cc_view* router_w, const cc_view* correction, int32_t top, int32_t n_groups,
+                        int32_t keep_groups, int32_t renormalise, cc_buf** ids_out, cc_buf** weights_out);
+/* out[t] = sum_s weights[t, s] * W_down[ids[t, s]] (act(W_gate[ids[t, s]] x[t]) * (W_up[ids[t, s]] x[t]))
+ * w_gate, w_up: [E * ff, D]; w_down: [E * D, ff] (expert-major stacks; F32 or BF16).  out: [T, D]. */
+CC_API int cc_moe_experts(cc_device* dev, const cc_view* x, const cc_view* ids, const cc_view* weights, const cc_view* w_gate, const cc_view* w_up,
+                          const cc_view* w_down, int32_t n_experts, int32_t ff, int32_t act, cc_buf** out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CRABML_SEQOPS_H */
