@@ -25,7 +25,7 @@ extern "C" CC_API int cc_tensor_dup(cc_device* dev, const cc_view* src, cc_buf**
 extern "C" CC_API int cc_tensor_export_f32(cc_device* dev, const cc_view* src, float* dst, size_t n) {   // cpu_tensor.rs:339-349
     CHECK_VIEW(dev, src, "export");
     if (!dst) return cc_fail(dev, CC_ERR_ARG, "export: dst is NULL");
-    REQUIRE_F32(dev, src, "export");
+    CC_REQUIRE(dev, src->buf->dtype == CC_F32 || src->buf->dtype == CC_I32, "export: not f32, but got type %d", src->buf->dtype);   // I32 index tensors: bit copy
     CC_REQUIRE(dev, view_contiguous(src), "export: tensor is not contiguous");
     FLUSH(dev);
     int64_t len = view_len(src);

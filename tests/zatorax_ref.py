@@ -51,6 +51,26 @@ def causal_conv(x, taps_w):
     return y
 
 
+def delta_rule(q, k, v, beta, decay, S0=None):
+    """The recurrence alone.  q, k [T, G, dk] (already normalised), v [T, H, dv], beta, decay [T, H]; per head, per token, in this order:
+    S <- decay S ; u = beta (v - S^T k) ; S <- S + k u^T ; o = S^T q.   -> (o [T, H, dv], final S [H, dk, dv])"""
+    T, G, dk = q.shape
+    H, dv = v.shape[1], v.shape[2]
+    rep = H // G
+    o = np.zeros((T, H, dv), F)
+    Sf = np.zeros((H, dk, dv), F)
+    for hd in range(H):
+        S = np.zeros((dk, dv), F) if S0 is None else np.array(S0[hd], F)
+        g = hd // rep
+        for t in range(T):
+            S = decay[t, hd] * S
+            u = beta[t, hd] * (v[t, hd] - S.T @ k[t, g])
+            S = S + np.outer(k[t, g], u)
+            o[t, hd] = S.T @ q[t, g]
+        Sf[hd] = S
+    return o, Sf
+
+
 def delta_mixer(h, w, p, m, eps):
     """Gated delta rule.  h [T, D]; w: weights; p: tensor prefix '<layer>.mix'; m: the layer's mixer config."""
     H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
@@ -63,16 +83,7 @@ def delta_mixer(h, w, p, m, eps):
     beta = sigmoid(linear(w[p + ".b"], h))                                                   # [T, H]
     decay = np.exp(-np.exp(np.asarray(w[p + ".A_log"], F))[None, :] * softplus(linear(w[p + ".a"], h) + np.asarray(w[p + ".dt_bias"], F)[None, :]))
     gate = silu(linear(w[p + ".g"], h)).reshape(T, H, dv)
-    o = np.zeros((T, H, dv), F)
-    rep = H // G
-    for hd in range(H):
-        S = np.zeros((dk, dv), F)
-        g = hd // rep
-        for t in range(T):
-            S = decay[t, hd] * S
-            u = beta[t, hd] * (v[t, hd] - S.T @ k[t, g])
-            S = S + np.outer(k[t, g], u)
-            o[t, hd] = S.T @ q[t, g]
+    o, _ = delta_rule(q, k, v, beta, decay)
     o = rms_unit(o, eps) * np.asarray(w[p + ".norm"], F)[None, None, :] * gate
     return linear(w[p + ".o"], o.reshape(T, H * dv))
 
@@ -86,15 +97,13 @@ def attention_keys_values(h, w, p, m, eps):
     return k, v
 
 
-def attention_mixer(h, w, p, m, eps, k, v):
-    """Sliding-window softmax attention with a logarithmic distance penalty.  k, v: [T, G, dk] / [T, G, dv] (own or borrowed)."""
-    H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    T = h.shape[0]
-    win, scale = m["mask"]["size"], F(m["scale"])
-    q = rms_unit(linear(w[p + ".q"], h).reshape(T, H, dk), eps) * np.asarray(w[p + ".q.norm"], F)[None, None, :]
-    r1, r2 = np.asarray(w[p + ".r1"], F), np.asarray(w[p + ".r2"], F)
-    out = np.zeros((T, H, dv), F)
+def windowed_softmax_attention(q, k, v, win, scale, r1, r2):
+    """q [T, H, dk] and k [T, G, dk] after their norms, v [T, G, dv].  Position i sees j with 0 <= i - j < win;
+    score = q.k * scale - r1[h] * ln(1 + r2[h] * (i - j)); ordinary softmax over the visible keys."""
+    T, H, _ = q.shape
+    G, dv = k.shape[1], v.shape[2]
     rep = H // G
+    out = np.zeros((T, H, dv), F)
     for i in range(T):
         lo = max(0, i - win + 1)
         dist = (i - np.arange(lo, i + 1)).astype(F)
@@ -103,6 +112,16 @@ def attention_mixer(h, w, p, m, eps, k, v):
             s = (k[lo:i + 1, g] @ q[i, hd]) * scale - r1[hd] * np.log1p(r2[hd] * dist)
             e = np.exp(s - s.max())
             out[i, hd] = (e / e.sum()) @ v[lo:i + 1, g]
+    return out
+
+
+def attention_mixer(h, w, p, m, eps, k, v):
+    """Sliding-window softmax attention with a logarithmic distance penalty.  k, v: [T, G, dk] / [T, G, dv] (own or borrowed)."""
+    H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    T = h.shape[0]
+    win, scale = m["mask"]["size"], F(m["scale"])
+    q = rms_unit(linear(w[p + ".q"], h).reshape(T, H, dk), eps) * np.asarray(w[p + ".q.norm"], F)[None, None, :]
+    out = windowed_softmax_attention(q, k, v, win, scale, np.asarray(w[p + ".r1"], F), np.asarray(w[p + ".r2"], F))
     return linear(w[p + ".o"], out.reshape(T, H * dv))
 
 
