@@ -6,6 +6,7 @@
 // tokens share the call (no atomics, no order that depends on the batch).  BF16 expert weights round the operand row to bfloat16
 // (x for gate / up, the hidden row for down) and accumulate in f32, exactly like cc_matmul_vec does for BF16 matrices.
 #include <cuda_bf16.h>
+#include <stdlib.h>
 
 #include "../../include/crabml_seqops.h"
 #include "capi_checks.cuh"
@@ -190,6 +191,95 @@ static int moe_launch(cc_device* dev, const float* x, const int* ids, const floa
     return CC_OK;
 }
 
+// ---- grouped path (BF16 weights, many rows): the (token, slot) rows are sorted by expert and every expert's rows run through the
+// tensor-core pipeline of prefill_gemm.cu in ONE grouped launch per projection.  A row's products and the order of its k sum do not
+// depend on its neighbours in the tile, and the slots are combined in slot order, so a token's result is still independent of the batch.
+bool cc_grouped_bf16_supported(int64_t m, int64_t k);
+int cc_launch_grouped_bf16(cc_device* dev, const cc_buf* w_stack, int64_t n_groups, int64_t m, int64_t k, const void* x_bf16, int64_t n_rows, const int* groups_dev,
+                           int max_tiles, int block_n, float* out);
+
+// one CTA: counts per expert (shared-memory atomics), exclusive offsets, the tile table {n_tiles | expert, first row, rows, 0 ...}, and
+// pos[i] = sorted row of entry i = (token, slot).  The order of the rows INSIDE an expert is arbitrary; no value depends on it.
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ ids, int n, int E, int block_n, int* __restrict__ pos, int* __restrict__ table) {
+    extern __shared__ int ms_sm[];            // counts[E], offsets[E]
+    int* cnt = ms_sm;
+    int* off = ms_sm + E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) pos[i] = atomicAdd(&cnt[ids[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int o = 0, nt = 0;
+        for (int e = 0; e < E; e++) {
+            off[e] = o;
+            for (int r = 0; r < cnt[e]; r += block_n) {
+                int* t = table + 4 + 4 * nt++;
+                t[0] = e; t[1] = o + r; t[2] = min(block_n, cnt[e] - r); t[3] = 0;
+            }
+            o += cnt[e];
+        }
+        table[0] = nt;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) pos[i] += off[ids[i]];
+}
+// xs[pos[i]][:] = bf16(x[i / top][:]) ; one warp per entry
+__global__ void moe_gather_bf16_kernel(const float* __restrict__ x, const int* __restrict__ pos, __nv_bfloat16* __restrict__ xs, int n, int top, int D) {
+    const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (i >= n) return;
+    const float* src = x + (int64_t)(i / top) * D;
+    __nv_bfloat16* dst = xs + (int64_t)pos[i] * D;
+    for (int d = lane * 2; d < D; d += 64) *(__nv_bfloat162*)(dst + d) = __floats2bfloat162_rn(src[d], src[d + 1]);
+}
+__global__ void moe_glu_bf16_kernel(const float* __restrict__ g, const float* __restrict__ u, __nv_bfloat16* __restrict__ h, int64_t n, int act) {
+    const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+    if (i >= n) return;
+    *(__nv_bfloat162*)(h + i) = __floats2bfloat162_rn(moe_act(g[i], act) * u[i], moe_act(g[i + 1], act) * u[i + 1]);
+}
+// out[t][d] = sum over the slots, in slot order, of weights[t][s] * y[pos[t * top + s]][d]
+__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos, const float* __restrict__ wts, float* __restrict__ out, int64_t T, int top, int D) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= T * D) return;
+    const int64_t t = i / D; const int d = (int)(i % D);
+    float acc = 0.0f;
+    for (int s = 0; s < top; s++) acc = fmaf(wts[t * top + s], y[(int64_t)pos[t * top + s] * D + d], acc);
+    out[i] = acc;
+}
+
+static int moe_grouped(cc_device* dev, const float* x, const int* ids, const float* wts, const cc_buf* wg, const cc_buf* wu, const cc_buf* wd, float* out, int64_t T, int D,
+                       int ff, int top, int E, int act) {
+    const int64_t n = T * top;
+    const int block_n = n / E >= 96 ? 128 : 64;
+    const int max_tiles = (int)((n + block_n - 1) / block_n) + E;
+    // one pool block: pos[n] | table[4 + 4 * max_tiles] | xs bf16 [n][D] | g f32 [n][ff] | u f32 [n][ff] | h bf16 [n][ff] | y f32 [n][D]
+    auto al = [](size_t v) { return (v + 255) & ~(size_t)255; };
+    const size_t o_pos = 0, o_tab = al((size_t)n * 4), o_xs = o_tab + al((size_t)(4 + 4 * max_tiles) * 4), o_g = o_xs + al((size_t)n * D * 2), o_u = o_g + al((size_t)n * ff * 4),
+                 o_h = o_u + al((size_t)n * ff * 4), o_y = o_h + al((size_t)n * ff * 2), total = o_y + al((size_t)n * D * 4);
+    uint8_t* base = nullptr; size_t cls = 0;
+    int rc = cc_pool_alloc(dev, total, (void**)&base, &cls);
+    if (rc) return rc;
+    int* pos = (int*)(base + o_pos); int* table = (int*)(base + o_tab);
+    __nv_bfloat16* xs = (__nv_bfloat16*)(base + o_xs); float* g = (float*)(base + o_g); float* u = (float*)(base + o_u);
+    __nv_bfloat16* h = (__nv_bfloat16*)(base + o_h); float* y = (float*)(base + o_y);
+    moe_sort_kernel<<<1, 1024, (size_t)2 * E * 4, dev->stream>>>(ids, (int)n, E, block_n, pos, table);
+    dev->launches++;
+    moe_gather_bf16_kernel<<<(unsigned)((n + 7) / 8), 256, 0, dev->stream>>>(x, pos, xs, (int)n, top, D);
+    dev->launches++;
+    rc = cc_launch_grouped_bf16(dev, wg, E, ff, D, xs, n, table, max_tiles, block_n, g);
+    if (!rc) rc = cc_launch_grouped_bf16(dev, wu, E, ff, D, xs, n, table, max_tiles, block_n, u);
+    if (!rc) {
+        moe_glu_bf16_kernel<<<(unsigned)((n * ff / 2 + 255) / 256), 256, 0, dev->stream>>>(g, u, h, n * ff, act);
+        dev->launches++;
+        rc = cc_launch_grouped_bf16(dev, wd, E, D, ff, h, n, table, max_tiles, block_n, y);
+    }
+    if (!rc) {
+        moe_combine_kernel<<<(unsigned)((T * D + 255) / 256), 256, 0, dev->stream>>>(y, pos, wts, out, T, top, D);
+        CC_LAUNCH_CHECK(dev);
+    }
+    cc_pool_free(dev, base, cls);
+    return rc;
+}
+
 extern "C" CC_API int cc_moe_experts(cc_device* dev, const cc_view* x, const cc_view* ids, const cc_view* weights, const cc_view* w_gate, const cc_view* w_up,
                                      const cc_view* w_down, int32_t n_experts, int32_t ff, int32_t act, cc_buf** out) {
     MOE_ENTER(dev, "moe_experts");
@@ -210,6 +300,11 @@ extern "C" CC_API int cc_moe_experts(cc_device* dev, const cc_view* x, const cc_
     if (rc) return rc;
     *out = o;
     if (T == 0) return CC_OK;
+    static const int grouped_min_rows = getenv("CRABML_MOE_GROUPED_MIN") ? atoi(getenv("CRABML_MOE_GROUPED_MIN")) : 128;
+    if (wt == CC_BF16 && T * top >= grouped_min_rows && n_experts <= 4096 && D % 2 == 0 && ff % 2 == 0 && cc_grouped_bf16_supported(ff, D) && cc_grouped_bf16_supported(D, ff) &&
+        ((uintptr_t)w_gate->buf->plane[0] & 15) == 0 && ((uintptr_t)w_up->buf->plane[0] & 15) == 0 && ((uintptr_t)w_down->buf->plane[0] & 15) == 0)
+        return moe_grouped(dev, (const float*)x->buf->plane[0], (const int*)ids->buf->plane[0], (const float*)weights->buf->plane[0], w_gate->buf, w_up->buf, w_down->buf,
+                           (float*)o->base, T, (int)D, ff, (int)top, n_experts, act);
     void* hid = nullptr; size_t cls = 0;
     rc = cc_pool_alloc(dev, (size_t)T * top * ff * 4, &hid, &cls);
     if (rc) return rc;

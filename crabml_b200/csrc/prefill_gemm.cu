@@ -90,7 +90,16 @@ struct PgShared {
 // than it delivers (profiles/r02e: 47 % tensor pipe with MT = 1).
 template <int BLOCK_N, int MT, int FMT = 0>
 __global__ void __launch_bounds__(PG_THREADS, 1) umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-                                                                  float* __restrict__ C, int m, int b, int k) {
+                                                                  float* __restrict__ C, int m, int b, int k, const int* __restrict__ groups = nullptr) {
+    // grouped mode (groups != nullptr; routed experts, moe.cu): groups[0] = number of tiles, then per tile {group, first row, rows, 0}.
+    // Tile y multiplies rows [first, first + rows) of X with the weight rows [group * m, (group + 1) * m) of the stacked W; m is the
+    // per-group row count.  Rows a tile loads beyond its own (the next group's, or zero fill) are computed and never stored.
+    int g_row0 = 0, g_w0 = 0;
+    if (groups) {
+        if ((int)blockIdx.y >= groups[0]) return;
+        const int* gt = groups + 4 + 4 * blockIdx.y;
+        g_w0 = gt[0] * m; g_row0 = gt[1]; b = gt[1] + gt[2];
+    }
     extern __shared__ __align__(1024) uint8_t pg_smem_raw[];
     __shared__ PgShared sh;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -99,7 +108,7 @@ __global__ void __launch_bounds__(PG_THREADS, 1) umma_gemm_kernel(const __grid_c
     constexpr int STAGES = (A_BYTES + B_BYTES) * PG_STAGES <= 200 * 1024 ? PG_STAGES : 3;
     uint8_t* ring = (uint8_t*)(((uintptr_t)pg_smem_raw + 1023) & ~(uintptr_t)1023);
     const int num_kb = k / PG_BLOCK_K;
-    const int m0 = blockIdx.x * PG_BLOCK_M * MT, n0 = blockIdx.y * BLOCK_N;
+    const int m0 = blockIdx.x * PG_BLOCK_M * MT, n0 = groups ? g_row0 : blockIdx.y * BLOCK_N;
 
     if (warp == 0 && lane == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_w) : "memory");
@@ -130,7 +139,7 @@ __global__ void __launch_bounds__(PG_THREADS, 1) umma_gemm_kernel(const __grid_c
                 pg_mbar_expect_tx(full, A_BYTES + B_BYTES);
                 uint8_t* st = ring + (size_t)s * (A_BYTES + B_BYTES);
 #pragma unroll
-                for (int t = 0; t < MT; t++) pg_tma_load_2d(pg_smem(st + t * A_TILE), &tmap_w, full, kb * PG_BLOCK_K, m0 + t * PG_BLOCK_M);
+                for (int t = 0; t < MT; t++) pg_tma_load_2d(pg_smem(st + t * A_TILE), &tmap_w, full, kb * PG_BLOCK_K, g_w0 + m0 + t * PG_BLOCK_M);
                 pg_tma_load_2d(pg_smem(st + A_BYTES), &tmap_x, full, kb * PG_BLOCK_K, n0);
             }
         }
@@ -379,4 +388,35 @@ int cc_launch_prefill_bf16(cc_device* dev, const cc_buf* w, const float* x_f32, 
     if (block_n == 256) return mt2 ? pg_launch<256, 2, 1>(dev, tw, tx, out, m, b, k) : pg_launch<256, 1, 1>(dev, tw, tx, out, m, b, k);
     if (block_n == 128) return mt2 ? pg_launch<128, 2, 1>(dev, tw, tx, out, m, b, k) : pg_launch<128, 1, 1>(dev, tw, tx, out, m, b, k);
     return mt2 ? pg_launch<64, 2, 1>(dev, tw, tx, out, m, b, k) : pg_launch<64, 1, 1>(dev, tw, tx, out, m, b, k);
+}
+
+// ---- grouped products of the routed feed-forward (moe.cu): X rows sorted by group, W = group-major stack [groups * m][k] ------------------
+bool cc_grouped_bf16_supported(int64_t m, int64_t k) {
+    static const bool off = getenv("CRABML_PREFILL_OFF") != nullptr;
+    return !off && m >= 1 && k >= PG_BLOCK_K && k % PG_BLOCK_K == 0;
+}
+// x_bf16: [n_rows][k] bfloat16, already sorted; groups_dev: the tile table (see the kernel); max_tiles: an upper bound of its length;
+// block_n: 64 or 128, the row count the table was cut for; out: f32 [n_rows][m]
+int cc_launch_grouped_bf16(cc_device* dev, const cc_buf* w_stack, int64_t n_groups, int64_t m, int64_t k, const void* x_bf16, int64_t n_rows, const int* groups_dev,
+                           int max_tiles, int block_n, float* out) {
+    CUtensorMap tw, tx;
+    int rc = pg_make_tmap(dev, &tw, w_stack->plane[0], n_groups * m, k, PG_BLOCK_M, true);
+    if (rc) return rc;
+    rc = pg_make_tmap(dev, &tx, x_bf16, n_rows, k, block_n, true);
+    if (rc) return rc;
+    const bool mt2 = m >= 512;
+#define PG_GROUPED(BN, MT)                                                                                                                       \
+    do {                                                                                                                                         \
+        const size_t stage = (size_t)MT * PG_BLOCK_M * PG_BLOCK_K * 2 + (size_t)BN * PG_BLOCK_K * 2;                                             \
+        const int stages = stage * PG_STAGES <= 200 * 1024 ? PG_STAGES : 3;                                                                      \
+        const size_t smem = (size_t)stages * stage + 1024;                                                                                       \
+        CC_CUDA(dev, cudaFuncSetAttribute(umma_gemm_kernel<BN, MT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                  \
+        dim3 grid((unsigned)((m + PG_BLOCK_M * MT - 1) / (PG_BLOCK_M * MT)), (unsigned)max_tiles);                                               \
+        umma_gemm_kernel<BN, MT, 1><<<grid, PG_THREADS, smem, dev->stream>>>(tw, tx, out, (int)m, 0, (int)k, groups_dev);                          \
+    } while (0)
+    if (block_n == 128) { if (mt2) PG_GROUPED(128, 2); else PG_GROUPED(128, 1); }
+    else { if (mt2) PG_GROUPED(64, 2); else PG_GROUPED(64, 1); }
+#undef PG_GROUPED
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
 }

@@ -208,13 +208,25 @@ def test_router_against_reference(dev, E, top, groups, keep):
 
 
 @pytest.mark.parametrize("dtype", [capi.F32, capi.BF16])
-def test_experts_weighted_sum(dev, dtype):
+@pytest.mark.parametrize("T,D,E,ff,top", [(19, 40, 5, 28, 2), (200, 128, 6, 64, 3), (333, 64, 3, 192, 1), (70, 192, 40, 64, 4)])
+def test_experts_weighted_sum(dev, dtype, T, D, E, ff, top):
+    """few rows: one warp per hidden row; many rows of BF16 weights with 64-aligned sizes: rows sorted by expert through the grouped
+    tensor-core product (experts with no row, with one row and with several tiles of rows all occur)"""
     from crabml_b200 import CudaTensor
-    rng = np.random.default_rng(5)
-    T, D, E, ff, top = 19, 40, 5, 28, 2
+    rng = np.random.default_rng(5 + T)
     x = rng.standard_normal((T, D)).astype(np.float32)
     wg = bf16(rng.standard_normal((E, ff, D)) / np.sqrt(D)); wu = bf16(rng.standard_normal((E, ff, D)) / np.sqrt(D)); wd = bf16(rng.standard_normal((E, D, ff)) / np.sqrt(ff))
-    ids = np.stack([rng.permutation(E)[:top] for _ in range(T)]).astype(np.int32)
+    pool = np.array([e for e in range(E) if e != 1])            # expert 1 gets no row at all
+    ids = np.stack([rng.permutation(pool)[:top] for _ in range(T)]).astype(np.int32)
+    if top < len(pool):
+        ids[ids == pool[-1]] = pool[0]
+        ids[0, 0] = pool[-1]                                     # and the last one exactly one row (the others of row 0 differ from it)
+        for t in range(T):                                       # keep a token's experts distinct
+            seen = set()
+            for s_ in range(top):
+                while int(ids[t, s_]) in seen:
+                    ids[t, s_] = pool[(int(np.where(pool == ids[t, s_])[0][0]) + 1) % (len(pool) - 1)]
+                seen.add(int(ids[t, s_]))
     wts = rng.uniform(0.1, 0.6, (T, top)).astype(np.float32)
     want = np.zeros((T, D))
     for t in range(T):
@@ -224,7 +236,15 @@ def test_experts_weighted_sum(dev, dtype):
     tid = CudaTensor.from_cpu(ids, [T, top], capi.I32, dev)
     got = seqops.moe_experts(T32(dev, x), tid, T32(dev, wts), W(dev, wg.reshape(E * ff, D), dtype), W(dev, wu.reshape(E * ff, D), dtype), W(dev, wd.reshape(E * D, ff), dtype),
                              E, ff).export().reshape(T, D)
-    assert np.abs(got - want).max() < (2e-5 if dtype == capi.F32 else 3e-2)
+    if dtype == capi.BF16:            # the product path rounds x and the hidden row to bfloat16: do the same to the reference
+        want = np.zeros((T, D))
+        for t in range(T):
+            for s in range(top):
+                e = ids[t, s]
+                xb = bf16(x[t]).astype(np.float64)
+                hrow = np.float32(R.silu((wg[e].astype(np.float64) @ xb).astype(np.float32).astype(np.float64))) * (wu[e].astype(np.float64) @ xb).astype(np.float32)
+                want[t] += wts[t, s] * (wd[e].astype(np.float64) @ bf16(hrow).astype(np.float64))
+    assert np.abs(got - want).max() < (2e-5 if dtype == capi.F32 else 2e-2)
 
 
 def test_bad_arguments_are_tensor_errors(dev):
