@@ -36,6 +36,9 @@ WORKLOADS = {
     # BASELINE.json config 5: the dense matmuls of a 4096-token prefill (TMA + tcgen05 path, csrc/prefill_gemm.cu); see run_prefill
     "mistral-7b-q8_0-prefill": ("MISTRAL_7B", "Q8_0", "Q8_0"),
     "llama2-7b-q8_0-prefill": ("LLAMA2_7B", "Q8_0", "Q8_0"),
+    # the Zatorax family at layer sizes of a real model (random weights), beside a llama stack of equal size; see run_zatorax
+    "zatorax-w1024": ("ZATORAX", "BF16", "BF16"),
+    "zatorax-w2048": ("ZATORAX", "BF16", "BF16"),
 }
 # dram bytes per megakernel launch from the committed ncu --set full capture (profiles/); None until captured
 TRAFFIC = {("llama2-7b-q8_0", 1): 7040893000 + 49879296}     # profiles/r02p_mega_ring_q8_0_ncu_raw.csv (mega_ring_kernel: dram__bytes_read.sum + dram__bytes_write.sum)
@@ -526,6 +529,108 @@ def run_prefill(args, rank, world, local_rank):
     dev.close()
 
 
+def zatorax_bench_config(width: int, n_layers: int = 4, vocab: int = 32000):
+    """delta, attention, attention reading the previous layer's keys / values, delta; 128-wide heads, 4 query heads per key head,
+    16 experts of width/2 (top 4) plus a shared expert of the model's width: 3 x width of active feed-forward per token"""
+    H = width // 128
+    G = max(1, H // 4)
+    mlp = {"kind": "moe", "expert": {"ff": width // 2}, "router": {"experts": 16, "top": 4, "groups": {"count": 4, "keep": 2}}, "shared": {"ff": width}}
+    delta = {"type": "delta", "mixer": {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "conv": 4}, "mlp": mlp}
+    layers = []
+    for i in range(n_layers):
+        if i % 4 in (0, 3):
+            layers.append(delta)
+        else:
+            m = {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "mask": {"size": 1024}, "scale": 128 ** -0.5}
+            if i % 4 == 2:
+                m["kv_from"] = i - 1
+            layers.append({"type": "attention", "mixer": m, "mlp": mlp})
+    return {"architecture": "Zatorax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": layers}
+
+
+def run_zatorax(args, rank, world, local_rank):
+    """Prefill and decode throughput of the Zatorax family at real layer sizes, beside the closest existing model -- a llama stack of the
+    same width, depth, head layout and ACTIVE feed-forward width (Q8_0 weights, its serving format) -- through each family's runner.
+    A prefill step = one `--prefill-tokens` prompt through model.step (logits of the last position read back); a decode step = one token."""
+    from crabml_b200 import CudaTensorDevice, zatorax
+    from crabml_b200 import runner as R
+    if rank != 0:
+        return
+    width = int(args.workload.split("-w")[1])
+    conf = zatorax.parse_config(zatorax_bench_config(width))
+    Tp, K, W = args.prefill_tokens, args.steps, args.warmup
+    rng = np.random.default_rng(SEED)
+    prompt = [int(v) for v in rng.integers(0, conf["vocab"], Tp)]
+    sampler = ClockSampler(local_rank); sampler.start()
+    out = {}
+    dev = CudaTensorDevice(local_rank, lazy=0)
+    model = zatorax.ZatoraxModel(dev, conf, zatorax.random_weights(conf, SEED), "bfloat16", chunk=args.zatorax_chunk)
+    params = sum(int(np.prod(sh)) if sh else 1 for sh in zatorax.expected_tensors(conf).values())
+    l0 = dev.launch_count()
+    for rep in range(2):                                             # first pass warms up (tensor maps, pool, function attributes)
+        slot = model.open()
+        dev.synchronize(); dev.timer_begin(); t0 = time.perf_counter()
+        model.step(slot, prompt, [Tp - 1])
+        pre_ms = dev.timer_end(); pre_wall = (time.perf_counter() - t0) * 1e3
+        if rep == 0:
+            model.close_seq(slot)
+    pre_launches = (dev.launch_count() - l0) // 2
+    tok = prompt[-1]
+    for _ in range(W):
+        model.step(slot, [tok], [0])
+    l0 = dev.launch_count()
+    dev.synchronize(); dev.timer_begin(); t0 = time.perf_counter()
+    for _ in range(K):
+        lg = model.step(slot, [tok], [0])                            # token id host -> device, logits device -> host, every step
+        tok = int(np.argmax(lg[0]))
+    dec_ms = dev.timer_end(); dec_wall = (time.perf_counter() - t0) * 1e3
+    dec_launches = dev.launch_count() - l0
+    out["zatorax"] = {"params": params, "prefill_tok_s": Tp / (pre_ms * 1e-3), "prefill_ms": pre_ms, "prefill_wall_ms": pre_wall, "prefill_launches": int(pre_launches),
+                      "decode_tok_s": K / (dec_ms * 1e-3), "decode_ms_per_token": dec_ms / K, "decode_wall_ms_per_token": dec_wall / K,
+                      "decode_launches_per_token": dec_launches / K, "state": model.stats()}
+    model.close(); dev.close()
+    # the closest existing model at equal size
+    H = width // 128
+    lconf = R.LlamaConfig(H, max(1, H // 4), len(conf["layers"]), width, 3 * width, Tp + K + W + 8, conf["vocab"], 1e-5, 128)
+    for lazy in (0, 2):
+        dev = CudaTensorDevice(local_rank, lazy=lazy)
+        weights = R.synthetic_weights(dev, lconf, TYPE_ID["Q8_0"], TYPE_ID["Q8_0"], seed=SEED)
+        r = R.LlamaRunner(dev, lconf, weights, Tp + K + W + 8)
+        rec = {}
+        if lazy == 0:
+            r.forward(prompt[:64], 0)                                   # warm-up of the batched path, then a fresh runner for the timed prompt
+            r.close()
+            r = R.LlamaRunner(dev, lconf, weights, Tp + K + W + 8)
+            dev.synchronize(); dev.timer_begin()
+            r.forward(prompt, 0)
+            rec["prefill_ms"] = dev.timer_end()
+            rec["prefill_tok_s"] = Tp / (rec["prefill_ms"] * 1e-3)
+            pos = Tp
+        else:
+            for i, t in enumerate(prompt[:32]):
+                r.forward([t], i, export=False)
+            pos = 32
+        for _ in range(W):
+            r.forward([prompt[0]], pos); pos += 1
+        l0 = dev.launch_count()
+        dev.synchronize(); dev.timer_begin()
+        for _ in range(K):
+            r.forward([prompt[0]], pos); pos += 1
+        ms = dev.timer_end()
+        rec.update({"decode_tok_s": K / (ms * 1e-3), "decode_ms_per_token": ms / K, "decode_launches_per_token": (dev.launch_count() - l0) / K, "kv_len_at_decode": pos})
+        out["llama_q8_0_lazy%d" % lazy] = rec
+        r.close(); dev.close()
+    clocks = sampler.stop()
+    z = out["zatorax"]
+    line = {"metric": "decode_tokens_per_s", "value": z["decode_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": z["decode_ms_per_token"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 matrices and product inputs, f32 everything else", "data": "synthetic",
+            "config": {"workload": args.workload, "model": zatorax_bench_config(width), "prefill_tokens": Tp, "chunk": args.zatorax_chunk,
+                       "closest_model": {"family": "llama", "weights": "Q8_0", "n_layers": lconf.n_layers, "dim": width, "hidden_dim": 3 * width, "heads": H, "kv_heads": lconf.n_kv_heads}},
+            "e2e": {"value": K / (z["decode_wall_ms_per_token"] * K * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": conf["vocab"] * 4},
+            "gpu_launches": int(dec_launches), "detail": out, "clocks": clocks}
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -540,12 +645,15 @@ def main():
     ap.add_argument("--no-also", action="store_true", help="skip the second (Q4_0) measurement of the default run")
     ap.add_argument("--multi", default="sharded", choices=["sharded", "replicas"], help="N > 1: shard one token stream (strong scaling, default) or run N independent replicas")
     ap.add_argument("--comm", default="p2p", choices=["p2p", "nccl"], help="exchange transport of the sharded path: one-shot NVLink peer stores (default) or the NCCL baseline")
+    ap.add_argument("--zatorax-chunk", type=int, default=512, help="zatorax workloads: longest run of prompt tokens one pass takes")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+    elif args.workload.startswith("zatorax-"):
+        run_zatorax(args, rank, world, local_rank)
     elif args.workload.endswith("-prefill"):
         run_prefill(args, rank, world, local_rank)
     else:

@@ -23,7 +23,7 @@
     } while (0)
 
 // ---- router ---------------------------------------------------------------------------------------------------------------------------
-// one warp per token.  Shared memory per warp: s[E] (softmax scores), c[E] (choice scores, -inf once taken or masked), gs[n_groups].
+// Shared memory per token: s[E] (softmax scores), c[E] (choice scores, -inf once taken or masked), gs[n_groups].
 // Ties go to the lowest index.
 __device__ __forceinline__ void warp_argmax(float& v, int& idx) {
 #pragma unroll
@@ -33,28 +33,30 @@ __device__ __forceinline__ void warp_argmax(float& v, int& idx) {
         if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
     }
 }
-#define RT_WARPS 4
+#define RT_WARPS 8
+// one CTA per token: its warps share the experts' logits (a warp per expert, lanes striding D), then warp 0 does the softmax and the choice
 __global__ void __launch_bounds__(RT_WARPS * 32) moe_route_kernel(const float* __restrict__ x, const float* __restrict__ wr, const float* __restrict__ corr,
                                                                   int* __restrict__ ids, float* __restrict__ wts, int T, int D, int E, int top, int n_groups, int keep,
                                                                   int renorm) {
     extern __shared__ float rt_sm[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * RT_WARPS + warp;
-    if (t >= T) return;
-    const int per_warp = 2 * E + (n_groups > 1 ? n_groups : 0);
-    float* s = rt_sm + (size_t)warp * per_warp;
+    const int t = blockIdx.x;
+    float* s = rt_sm;
     float* c = s + E;
     float* gs = c + E;
     const float* xr = x + (int64_t)t * D;
-    float mx = -INFINITY;
-    for (int e = 0; e < E; e++) {
+    for (int e = warp; e < E; e += RT_WARPS) {
         const float* w = wr + (int64_t)e * D;
         float acc = 0.0f;
         for (int d = lane; d < D; d += 32) acc = fmaf(w[d], xr[d], acc);
         acc = warp_sum(acc);
         if (lane == 0) s[e] = acc;
-        mx = fmaxf(mx, acc);
     }
+    __syncthreads();
+    if (warp != 0) return;
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
+    mx = warp_max(mx);
     __syncwarp();
     float sum = 0.0f;
     for (int e = lane; e < E; e += 32) { const float v = expf(s[e] - mx); s[e] = v; sum += v; }
@@ -116,10 +118,10 @@ extern "C" CC_API int cc_moe_route(cc_device* dev, const cc_view* x, const cc_vi
     if (rc) { cc_tensor_release(ids); return rc; }
     *ids_out = ids; *weights_out = wts;
     if (T == 0) return CC_OK;
-    const size_t smem = (size_t)RT_WARPS * (2 * E + (n_groups > 1 ? n_groups : 0)) * 4;
+    const size_t smem = (size_t)(2 * E + (n_groups > 1 ? n_groups : 0)) * 4;
     if (smem > 200 * 1024) return cc_fail(dev, CC_ERR_UNSUPPORTED, "moe_route: %lld experts need %zu bytes of shared memory", (long long)E, smem);
     if (smem > 48 * 1024) CC_CUDA(dev, cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    moe_route_kernel<<<(unsigned)((T + RT_WARPS - 1) / RT_WARPS), RT_WARPS * 32, smem, dev->stream>>>((const float*)x->buf->plane[0], (const float*)router_w->buf->plane[0],
+    moe_route_kernel<<<(unsigned)T, RT_WARPS * 32, smem, dev->stream>>>((const float*)x->buf->plane[0], (const float*)router_w->buf->plane[0],
                                                                                                      correction ? (const float*)correction->buf->plane[0] : nullptr,
                                                                                                      (int*)ids->base, (float*)wts->base, (int)T, (int)D, (int)E, top, n_groups,
                                                                                                      keep_groups, renormalise);

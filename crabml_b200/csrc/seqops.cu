@@ -194,44 +194,79 @@ __global__ void delta_gates_kernel(const float* __restrict__ a, const float* __r
 // DK == 0 (any dk) in shared memory [dk][DR_THREADS].  Tokens run in order; per token two passes over dk:
 //   acc = sum_i S[i] k[i]           (the decayed read-out is decay * acc)
 //   u = beta * (v - decay * acc) ;  S[i] = decay * S[i] + k[i] * u ;  out = sum_i S[i] q[i]
-// k and q of the token are read at warp-uniform addresses (one broadcast transaction per load).
+// k and q of DR_TB tokens at a time are staged in shared memory (one trip to L2 per block of tokens instead of one per token).  Both
+// dot products run as four interleaved partial sums (i mod 4), added as (p0 + p1) + (p2 + p3): a fixed order, the same for any T.
 #define DR_THREADS 64
+#define DR_TB 8
 template <int DK>
 __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                                                                 const float* __restrict__ bd, float* __restrict__ state, float* __restrict__ o, int T, int H, int G,
                                                                 int dk, int dv) {
-    extern __shared__ float dr_sm[];
+    extern __shared__ float dr_sm[];                          // k[DR_TB][dk4], q[DR_TB][dk4], then (DK == 0) the state columns
+    const int dk4 = (dk + 3) & ~3;
+    float* skq = dr_sm;
     const int h = blockIdx.x, g = h / (H / G);
     const int j = blockIdx.y * DR_THREADS + threadIdx.x;
     const bool live = j < dv;
     const int jj = live ? j : dv - 1;                       // idle threads shadow the last column and never store
     float S[DK > 0 ? DK : 1];
-    float* Ss = dr_sm + threadIdx.x;                         // generic: S[i] at Ss[i * DR_THREADS]
+    float* Ss = dr_sm + 2 * DR_TB * dk4 + threadIdx.x;       // generic: S[i] at Ss[i * DR_THREADS]
     float* sp = state + ((int64_t)h * dk) * dv + jj;
     if (DK > 0) {
 #pragma unroll
         for (int i = 0; i < DK; i++) S[i] = sp[(int64_t)i * dv];
     } else {
-        for (int i = 0; i < dk; i++) Ss[i * DR_THREADS] = sp[(int64_t)i * dv];
+        for (int i = 0; i < dk4; i++) Ss[i * DR_THREADS] = i < dk ? sp[(int64_t)i * dv] : 0.0f;
     }
-    for (int t = 0; t < T; t++) {
-        const float* kt = k + ((int64_t)t * G + g) * dk;
-        const float* qt = q + ((int64_t)t * G + g) * dk;
-        const float beta = bd[((int64_t)t * H + h) * 2], dec = bd[((int64_t)t * H + h) * 2 + 1];
-        const float vj = v[((int64_t)t * H + h) * dv + jj];
-        float acc = 0.0f, out = 0.0f;
-        if (DK > 0) {
-#pragma unroll
-            for (int i = 0; i < DK; i++) acc = fmaf(S[i], kt[i], acc);
-            const float u = beta * (vj - dec * acc);
-#pragma unroll
-            for (int i = 0; i < DK; i++) { S[i] = fmaf(kt[i], u, dec * S[i]); out = fmaf(S[i], qt[i], out); }
-        } else {
-            for (int i = 0; i < dk; i++) acc = fmaf(Ss[i * DR_THREADS], kt[i], acc);
-            const float u = beta * (vj - dec * acc);
-            for (int i = 0; i < dk; i++) { const float s = fmaf(kt[i], u, dec * Ss[i * DR_THREADS]); Ss[i * DR_THREADS] = s; out = fmaf(s, qt[i], out); }
+    for (int tb = 0; tb < T; tb += DR_TB) {
+        const int nt = min(DR_TB, T - tb);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nt * dk4; idx += DR_THREADS) {
+            const int tt = idx / dk4, i = idx - tt * dk4;
+            const int64_t src = ((int64_t)(tb + tt) * G + g) * dk + i;
+            skq[tt * dk4 + i] = i < dk ? k[src] : 0.0f;
+            skq[(DR_TB + tt) * dk4 + i] = i < dk ? q[src] : 0.0f;
         }
-        if (live) o[((int64_t)t * H + h) * dv + j] = out;
+        __syncthreads();
+        for (int tt = 0; tt < nt; tt++) {
+            const int t = tb + tt;
+            const float* kt = skq + tt * dk4;
+            const float* qt = skq + (DR_TB + tt) * dk4;
+            const float beta = bd[((int64_t)t * H + h) * 2], dec = bd[((int64_t)t * H + h) * 2 + 1];
+            const float vj = v[((int64_t)t * H + h) * dv + jj];
+            float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f, o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
+            if (DK > 0) {
+#pragma unroll
+                for (int i = 0; i < DK; i += 4) {
+                    const float4 kv = *(const float4*)(kt + i);
+                    a0 = fmaf(S[i], kv.x, a0); a1 = fmaf(S[i + 1], kv.y, a1); a2 = fmaf(S[i + 2], kv.z, a2); a3 = fmaf(S[i + 3], kv.w, a3);
+                }
+                const float u = beta * (vj - dec * ((a0 + a1) + (a2 + a3)));
+#pragma unroll
+                for (int i = 0; i < DK; i += 4) {
+                    const float4 kv = *(const float4*)(kt + i);
+                    const float4 qv = *(const float4*)(qt + i);
+                    S[i] = fmaf(kv.x, u, dec * S[i]); S[i + 1] = fmaf(kv.y, u, dec * S[i + 1]); S[i + 2] = fmaf(kv.z, u, dec * S[i + 2]); S[i + 3] = fmaf(kv.w, u, dec * S[i + 3]);
+                    o0 = fmaf(S[i], qv.x, o0); o1 = fmaf(S[i + 1], qv.y, o1); o2 = fmaf(S[i + 2], qv.z, o2); o3 = fmaf(S[i + 3], qv.w, o3);
+                }
+            } else {
+                for (int i = 0; i < dk4; i += 4) {
+                    const float4 kv = *(const float4*)(kt + i);
+                    a0 = fmaf(Ss[i * DR_THREADS], kv.x, a0); a1 = fmaf(Ss[(i + 1) * DR_THREADS], kv.y, a1);
+                    a2 = fmaf(Ss[(i + 2) * DR_THREADS], kv.z, a2); a3 = fmaf(Ss[(i + 3) * DR_THREADS], kv.w, a3);
+                }
+                const float u = beta * (vj - dec * ((a0 + a1) + (a2 + a3)));
+                for (int i = 0; i < dk4; i += 4) {
+                    const float4 kv = *(const float4*)(kt + i);
+                    const float4 qv = *(const float4*)(qt + i);
+                    const float s0 = fmaf(kv.x, u, dec * Ss[i * DR_THREADS]), s1 = fmaf(kv.y, u, dec * Ss[(i + 1) * DR_THREADS]);
+                    const float s2 = fmaf(kv.z, u, dec * Ss[(i + 2) * DR_THREADS]), s3 = fmaf(kv.w, u, dec * Ss[(i + 3) * DR_THREADS]);
+                    Ss[i * DR_THREADS] = s0; Ss[(i + 1) * DR_THREADS] = s1; Ss[(i + 2) * DR_THREADS] = s2; Ss[(i + 3) * DR_THREADS] = s3;
+                    o0 = fmaf(s0, qv.x, o0); o1 = fmaf(s1, qv.y, o1); o2 = fmaf(s2, qv.z, o2); o3 = fmaf(s3, qv.w, o3);
+                }
+            }
+            if (live) o[((int64_t)t * H + h) * dv + j] = (o0 + o1) + (o2 + o3);
+        }
     }
     if (live) {
         if (DK > 0) {
@@ -268,11 +303,13 @@ extern "C" CC_API int cc_gated_delta_rule(cc_device* dev, const cc_view* q, cons
     dev->launches++;
     dim3 grid((unsigned)H, (unsigned)((dv + DR_THREADS - 1) / DR_THREADS));
 #define DR_ARGS fptr(q), fptr(k), fptr(v), (const float*)bdp, fptr(state), (float*)o->base, (int)T, H, G, dk, dv
-    if (dk == 32) delta_rule_kernel<32><<<grid, DR_THREADS, 0, dev->stream>>>(DR_ARGS);
-    else if (dk == 64) delta_rule_kernel<64><<<grid, DR_THREADS, 0, dev->stream>>>(DR_ARGS);
-    else if (dk == 128) delta_rule_kernel<128><<<grid, DR_THREADS, 0, dev->stream>>>(DR_ARGS);
+    const int dk4 = (dk + 3) & ~3;
+    const size_t stage = (size_t)2 * DR_TB * dk4 * 4;
+    if (dk == 32) delta_rule_kernel<32><<<grid, DR_THREADS, stage, dev->stream>>>(DR_ARGS);
+    else if (dk == 64) delta_rule_kernel<64><<<grid, DR_THREADS, stage, dev->stream>>>(DR_ARGS);
+    else if (dk == 128) delta_rule_kernel<128><<<grid, DR_THREADS, stage, dev->stream>>>(DR_ARGS);
     else {
-        const size_t smem = (size_t)dk * DR_THREADS * 4;
+        const size_t smem = stage + (size_t)dk4 * DR_THREADS * 4;
         if (smem > 200 * 1024) { cc_pool_free(dev, bdp, cls); return cc_fail(dev, CC_ERR_UNSUPPORTED, "gated_delta_rule: dk=%d is too large", dk); }
         if (smem > 48 * 1024) CC_CUDA(dev, cudaFuncSetAttribute(delta_rule_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         delta_rule_kernel<0><<<grid, DR_THREADS, smem, dev->stream>>>(DR_ARGS);
@@ -324,66 +361,168 @@ extern "C" CC_API int cc_kv_ring_append(cc_device* dev, const cc_view* kring, co
     return CC_OK;
 }
 
-// grid (T, H), WA_THREADS threads.  Shared memory: q[dk] then one score per visible key.  Keys are dealt to warps round-robin; a warp's
-// lanes stride the head dimension and butterfly-reduce each dot product; the value sum of output column d runs over the keys in
-// ascending position.  The result for a query depends only on (query, visible keys), not on T.
-#define WA_THREADS 128
-__global__ void __launch_bounds__(WA_THREADS) window_attention_kernel(const float* __restrict__ q, const float* __restrict__ qnw, float eps, const float* __restrict__ kring,
-                                                                      const float* __restrict__ vring, float* __restrict__ out, int64_t pos0, int ring, int H, int G, int dk,
-                                                                      int dv, int window, float scale, const float* __restrict__ r1, const float* __restrict__ r2) {
-    extern __shared__ float wa_sm[];
-    __shared__ float red[WA_THREADS / 32];
-    float* sq = wa_sm;
-    float* sc = wa_sm + ((dk + 3) & ~3);
-    const int t = blockIdx.x, h = blockIdx.y, g = h / (H / G);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int64_t i = pos0 + t;
-    const int64_t lo = (window > 0 && i - window + 1 > 0) ? i - window + 1 : 0;
-    const int n = (int)(i - lo + 1);
-    // query head -> shared memory, RMS-normalised
-    const float* qr = q + ((int64_t)t * H + h) * dk;
+// Three kernels (plus the query norm), all plain 32-bit arithmetic, shaped as banded tile products so that keys and values are read once
+// per TILE of queries and once for all query heads of a key/value head, not once per (query, head):
+//   1. wa_scores_kernel : S[row][c] = (q_row . k_j) * scale - r1 ln(1 + r2 (i - j)) for the visible j = lo_i + c, a 64 x 64 tile product over dk
+//   2. wa_softmax_kernel: one warp per row: max, exp, sum, normalise (in place)
+//   3. wa_values_kernel : out[row][d] = sum_c S[row][c] v[lo_i + c][d], a 64 x 64 tile product over the keys of the tile's band
+// A row is one (query, head); a tile's 64 rows are the R = n_heads / n_kv heads of one key/value head for 64 / R consecutive queries.
+// Every dot product and every value sum runs over its index in ascending order inside ONE thread (masked keys add an exact 0), and the
+// softmax sums depend on the row alone: the result for a query does not depend on the tiling, on T, or on where the call starts.
+#define WA_TILE 64
+#define WA_K 16
+#define WA_THREADS 256
+struct WaGeom {
+    int T, H, G, R, dk, dv, window, ring, QT, cap;      // QT queries per tile; cap = row stride of S
+    int64_t pos0;
+};
+__device__ __forceinline__ int64_t wa_lo(const WaGeom& g, int64_t i) { return (g.window > 0 && i - g.window + 1 > 0) ? i - g.window + 1 : 0; }
+
+__global__ void head_rms_norm_kernel(float* __restrict__ x, const float* __restrict__ w, int64_t n_units, int hs, float eps) {
+    const int64_t u = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (u >= n_units) return;
+    float* xr = x + u * hs;
     float ss = 0.0f;
-    for (int c = threadIdx.x; c < dk; c += WA_THREADS) { const float x = qr[c]; sq[c] = x; ss = fmaf(x, x, ss); }
-    if (qnw) {
-        ss = warp_sum(ss);
-        if (lane == 0) red[warp] = ss;
+    for (int c = lane; c < hs; c += 32) ss = fmaf(xr[c], xr[c], ss);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)hs + eps);
+    for (int c = lane; c < hs; c += 32) xr[c] = xr[c] * inv * w[c];
+}
+
+// grid (key tiles of the band, query tiles, G)
+__global__ void __launch_bounds__(WA_THREADS) wa_scores_kernel(const float* __restrict__ q, const float* __restrict__ kring, float* __restrict__ S, WaGeom g, float scale,
+                                                               const float* __restrict__ r1, const float* __restrict__ r2) {
+    __shared__ float sq[WA_K][WA_TILE + 4];
+    __shared__ float sk[WA_K][WA_TILE + 4];
+    const int t0 = blockIdx.y * g.QT, kvh = blockIdx.z;
+    const int tq_n = min(g.QT, g.T - t0);
+    const int64_t i_first = g.pos0 + t0, i_last = i_first + tq_n - 1;
+    const int64_t band_lo = wa_lo(g, i_first);
+    const int64_t j0 = band_lo + (int64_t)blockIdx.x * WA_TILE;
+    if (j0 > i_last) return;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    float acc[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; a++)
+#pragma unroll
+        for (int b = 0; b < 4; b++) acc[a][b] = 0.0f;
+    for (int d0 = 0; d0 < g.dk; d0 += WA_K) {
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int idx = threadIdx.x + e * WA_THREADS;
+            const int r = idx >> 4, dd = idx & 15;
+            const int tq = r / g.R, hr = r - tq * g.R;
+            const bool din = d0 + dd < g.dk;
+            sq[dd][r] = (din && tq < tq_n) ? q[((int64_t)(t0 + tq) * g.H + kvh * g.R + hr) * g.dk + d0 + dd] : 0.0f;
+            const int64_t j = j0 + r;
+            sk[dd][r] = (din && j <= i_last) ? kring[((j % g.ring) * g.G + kvh) * g.dk + d0 + dd] : 0.0f;
+        }
         __syncthreads();
-        float tot = 0.0f;
-        for (int w = 0; w < WA_THREADS / 32; w++) tot += red[w];
-        const float inv = 1.0f / sqrtf(tot / (float)dk + eps);
-        for (int c = threadIdx.x; c < dk; c += WA_THREADS) sq[c] = sq[c] * inv * qnw[c];
+#pragma unroll
+        for (int dd = 0; dd < WA_K; dd++) {
+            const float4 qv = *(const float4*)&sq[dd][ty * 4];
+            const float4 kv = *(const float4*)&sk[dd][tx * 4];
+            const float qr[4] = {qv.x, qv.y, qv.z, qv.w}, kr[4] = {kv.x, kv.y, kv.z, kv.w};
+#pragma unroll
+            for (int a = 0; a < 4; a++)
+#pragma unroll
+                for (int b = 0; b < 4; b++) acc[a][b] = fmaf(qr[a], kr[b], acc[a][b]);
+        }
         __syncthreads();
-    } else __syncthreads();
-    const float hr1 = r1 ? r1[h] : 0.0f, hr2 = r2 ? r2[h] : 0.0f;
-    float mx = -INFINITY;
-    for (int jj = warp; jj < n; jj += WA_THREADS / 32) {
-        const int64_t p = lo + jj;
-        const float* kr = kring + ((p % ring) * G + g) * dk;
-        float d = 0.0f;
-        for (int c = lane; c < dk; c += 32) d = fmaf(sq[c], kr[c], d);
-        d = warp_sum(d);
-        float s = d * scale;
-        if (r1) s -= hr1 * log1pf(hr2 * (float)(i - p));
-        if (lane == 0) sc[jj] = s;
-        mx = fmaxf(mx, s);
     }
-    if (lane == 0) red[warp] = mx;
-    __syncthreads();
-    mx = red[0];
-    for (int w = 1; w < WA_THREADS / 32; w++) mx = fmaxf(mx, red[w]);
-    __syncthreads();
+#pragma unroll
+    for (int a = 0; a < 4; a++) {
+        const int r = ty * 4 + a;
+        const int tq = r / g.R, hr = r - tq * g.R;
+        if (tq >= tq_n) continue;
+        const int h = kvh * g.R + hr;
+        const int64_t i = i_first + tq, lo = wa_lo(g, i);
+        float* Sr = S + ((int64_t)(t0 + tq) * g.H + h) * g.cap;
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+            const int64_t j = j0 + tx * 4 + b;
+            if (j < lo || j > i) continue;
+            float sc = acc[a][b] * scale;
+            if (r1) sc -= r1[h] * log1pf(r2[h] * (float)(i - j));
+            Sr[j - lo] = sc;
+        }
+    }
+}
+// one warp per row
+__global__ void wa_softmax_kernel(float* __restrict__ S, WaGeom g) {
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= (int64_t)g.T * g.H) return;
+    const int64_t i = g.pos0 + row / g.H;
+    const int n = (int)(i - wa_lo(g, i) + 1);
+    float* Sr = S + row * g.cap;
+    float mx = -INFINITY;
+    for (int c = lane; c < n; c += 32) mx = fmaxf(mx, Sr[c]);
+    mx = warp_max(mx);
     float sum = 0.0f;
-    for (int jj = threadIdx.x; jj < n; jj += WA_THREADS) { const float e = expf(sc[jj] - mx); sc[jj] = e; sum += e; }
+    for (int c = lane; c < n; c += 32) { const float e = expf(Sr[c] - mx); Sr[c] = e; sum += e; }
     sum = warp_sum(sum);
-    if (lane == 0) red[warp] = sum;
-    __syncthreads();
-    float tot = 0.0f;
-    for (int w = 0; w < WA_THREADS / 32; w++) tot += red[w];
-    const float inv = 1.0f / tot;
-    for (int d = threadIdx.x; d < dv; d += WA_THREADS) {
-        float acc = 0.0f;
-        for (int jj = 0; jj < n; jj++) acc = fmaf(sc[jj], vring[(((lo + jj) % ring) * G + g) * dv + d], acc);
-        out[((int64_t)t * H + h) * dv + d] = acc * inv;
+    const float inv = 1.0f / sum;
+    for (int c = lane; c < n; c += 32) Sr[c] *= inv;
+}
+// grid (dv tiles, query tiles, G)
+__global__ void __launch_bounds__(WA_THREADS) wa_values_kernel(const float* __restrict__ S, const float* __restrict__ vring, float* __restrict__ out, WaGeom g) {
+    __shared__ float sp[WA_K][WA_TILE + 4];       // [key][row]
+    __shared__ float sv[WA_K][WA_TILE + 4];       // [key][dv column]
+    const int t0 = blockIdx.y * g.QT, kvh = blockIdx.z, c0 = blockIdx.x * WA_TILE;
+    const int tq_n = min(g.QT, g.T - t0);
+    const int64_t i_first = g.pos0 + t0, i_last = i_first + tq_n - 1;
+    const int64_t band_lo = wa_lo(g, i_first);
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    float acc[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; a++)
+#pragma unroll
+        for (int b = 0; b < 4; b++) acc[a][b] = 0.0f;
+    for (int64_t j0 = band_lo; j0 <= i_last; j0 += WA_K) {
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int idx = threadIdx.x + e * WA_THREADS;
+            {   // probabilities: consecutive threads read consecutive keys of one row
+                const int r = idx >> 4, kk = idx & 15;
+                const int tq = r / g.R, hr = r - tq * g.R;
+                float p = 0.0f;
+                if (tq < tq_n) {
+                    const int64_t i = i_first + tq, lo = wa_lo(g, i), j = j0 + kk;
+                    if (j >= lo && j <= i) p = S[((int64_t)(t0 + tq) * g.H + kvh * g.R + hr) * g.cap + (j - lo)];
+                }
+                sp[kk][r] = p;
+            }
+            {   // values: consecutive threads read consecutive columns of one key
+                const int kk = idx >> 6, c = idx & 63;
+                const int64_t j = j0 + kk;
+                sv[kk][c] = (j <= i_last && c0 + c < g.dv) ? vring[((j % g.ring) * g.G + kvh) * g.dv + c0 + c] : 0.0f;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < WA_K; kk++) {
+            const float4 pv = *(const float4*)&sp[kk][ty * 4];
+            const float4 vv = *(const float4*)&sv[kk][tx * 4];
+            const float pr[4] = {pv.x, pv.y, pv.z, pv.w}, vr[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+            for (int a = 0; a < 4; a++)
+#pragma unroll
+                for (int b = 0; b < 4; b++) acc[a][b] = fmaf(pr[a], vr[b], acc[a][b]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int a = 0; a < 4; a++) {
+        const int r = ty * 4 + a;
+        const int tq = r / g.R, hr = r - tq * g.R;
+        if (tq >= tq_n) continue;
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+            const int c = c0 + tx * 4 + b;
+            if (c < g.dv) out[((int64_t)(t0 + tq) * g.H + kvh * g.R + hr) * g.dv + c] = acc[a][b];
+        }
     }
 }
 extern "C" CC_API int cc_window_attention(cc_device* dev, const cc_view* q, const cc_view* qnw, float eps, const cc_view* kring, const cc_view* vring, int64_t pos0,
@@ -413,12 +552,30 @@ extern "C" CC_API int cc_window_attention(cc_device* dev, const cc_view* q, cons
     *out = o;
     if (T == 0) return CC_OK;
     const int64_t maxn = window > 0 ? (window < last + 1 ? window : last + 1) : last + 1;
-    const size_t smem = ((size_t)((dk + 3) & ~3) + (size_t)maxn) * 4;
-    if (smem > 200 * 1024) return cc_fail(dev, CC_ERR_UNSUPPORTED, "window_attention: %lld visible keys need %zu bytes of shared memory", (long long)maxn, smem);
-    if (smem > 48 * 1024) CC_CUDA(dev, cudaFuncSetAttribute(window_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    dim3 grid((unsigned)T, (unsigned)H);
-    window_attention_kernel<<<grid, WA_THREADS, smem, dev->stream>>>(fptr(q), qnw ? fptr(qnw) : nullptr, eps, fptr(kring), fptr(vring), (float*)o->base, pos0, (int)ring, H, G,
-                                                                   dk, dv, window, scale, r1 ? fptr(r1) : nullptr, r2 ? fptr(r2) : nullptr);
+    const int R = H / G;
+    CC_REQUIRE(dev, R <= WA_TILE, "window_attention: %d query heads per key/value head (at most %d)", R, WA_TILE);
+    WaGeom g;
+    g.T = (int)T; g.H = H; g.G = G; g.R = R; g.dk = dk; g.dv = dv; g.window = window; g.ring = (int)ring; g.QT = WA_TILE / R; g.cap = (int)maxn; g.pos0 = pos0;
+    float* qp = fptr(q);
+    if (qnw) {             // the query norm, in place: q is this call's private projection output in every caller of the runner; a caller that
+                           // needs its q untouched passes a copy
+        head_rms_norm_kernel<<<(unsigned)((T * H + 7) / 8), 256, 0, dev->stream>>>(qp, fptr(qnw), T * H, dk, eps);
+        dev->launches++;
+    }
+    void* Sp = nullptr; size_t cls = 0;
+    rc = cc_pool_alloc(dev, (size_t)T * H * maxn * 4, &Sp, &cls);
+    if (rc) return rc;
+    const int q_tiles = (int)((T + g.QT - 1) / g.QT);
+    const int64_t band = window > 0 ? (int64_t)window - 1 + g.QT : last + 1;          // keys a query tile can see
+    const int64_t band_max = band < last + 1 ? band : last + 1;
+    dim3 g1((unsigned)((band_max + WA_TILE - 1) / WA_TILE), (unsigned)q_tiles, (unsigned)G);
+    wa_scores_kernel<<<g1, WA_THREADS, 0, dev->stream>>>(qp, fptr(kring), (float*)Sp, g, scale, r1 ? fptr(r1) : nullptr, r2 ? fptr(r2) : nullptr);
+    dev->launches++;
+    wa_softmax_kernel<<<(unsigned)((T * H + 7) / 8), 256, 0, dev->stream>>>((float*)Sp, g);
+    dev->launches++;
+    dim3 g3((unsigned)((dv + WA_TILE - 1) / WA_TILE), (unsigned)q_tiles, (unsigned)G);
+    wa_values_kernel<<<g3, WA_THREADS, 0, dev->stream>>>((const float*)Sp, fptr(vring), (float*)o->base, g);
+    cc_pool_free(dev, Sp, cls);
     CC_LAUNCH_CHECK(dev);
     return CC_OK;
 }

@@ -60,7 +60,8 @@ CC_API int cc_gated_delta_rule(cc_device* dev, const cc_view* q, const cc_view* 
  * head is RMS-normalised (eps) and multiplied by it before it is stored. */
 CC_API int cc_kv_ring_append(cc_device* dev, const cc_view* kring, const cc_view* vring, const cc_view* k, const cc_view* v,
                              const cc_view* k_norm_w, float eps, int64_t pos0, int32_t n_kv, int32_t dk, int32_t dv);
-/* q: [T, n_heads * dk] raw queries of positions pos0 .. ; q_norm_w ([dk], may be NULL): per-head RMS norm (eps) times weight.
+/* q: [T, n_heads * dk] raw queries of positions pos0 .. ; q_norm_w ([dk], may be NULL): per-head RMS norm (eps) times weight, applied
+ * to q IN PLACE (q is the caller's projection output; pass a copy to keep the raw values).
  * Position i attends to j with 0 <= i - j < window (window <= 0: no limit but j >= 0); the ring must still hold those rows.
  *   score = (q . k) * scale - r1[h] * ln(1 + r2[h] * (i - j))        (r1, r2: [n_heads], both NULL = no distance term)
  * then softmax over the visible keys and the weighted sum of values.  out: [T, n_heads * dv]. */
