@@ -190,31 +190,37 @@ __global__ void delta_gates_kernel(const float* __restrict__ a, const float* __r
     bd[i * 2] = seq_sigmoid(b[i]);
     bd[i * 2 + 1] = expf(-expf(a_log[h]) * seq_softplus(a[i] + dt_bias[h]));
 }
-// grid (H, ceil(dv / DR_THREADS)); thread j owns column j of the head's state S[dk][dv] for the whole call: DK > 0 keeps it in registers,
-// DK == 0 (any dk) in shared memory [dk][DR_THREADS].  Tokens run in order; per token two passes over dk:
+// grid (H, ceil(dv / columns per CTA)).  A column j of the head's state S[dk][dv] is owned for the whole call by SPLIT adjacent threads,
+// each holding dk / SPLIT of its entries: DK > 0 keeps them in registers (SPLIT = 2 for dk = 128, so that 64 registers hold a thread's
+// share), DK == 0 (any dk) in shared memory [dk][DR_THREADS].  Tokens run in order; per token two passes over dk:
 //   acc = sum_i S[i] k[i]           (the decayed read-out is decay * acc)
 //   u = beta * (v - decay * acc) ;  S[i] = decay * S[i] + k[i] * u ;  out = sum_i S[i] q[i]
-// k and q of DR_TB tokens at a time are staged in shared memory (one trip to L2 per block of tokens instead of one per token).  Both
-// dot products run as four interleaved partial sums (i mod 4), added as (p0 + p1) + (p2 + p3): a fixed order, the same for any T.
+// k, q, beta and decay of DR_TB tokens at a time are staged in shared memory and the thread's v values in registers (one trip to L2 per
+// block of tokens instead of several per token).  Both dot products run as four interleaved partial sums per thread (i mod 4), added as
+// (p0 + p1) + (p2 + p3), then the SPLIT shares are added by a shuffle: a fixed order, the same for any T.
 #define DR_THREADS 64
-#define DR_TB 8
-template <int DK>
+#define DR_TB 16
+template <int DK, int SPLIT>
 __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                                                                 const float* __restrict__ bd, float* __restrict__ state, float* __restrict__ o, int T, int H, int G,
                                                                 int dk, int dv) {
-    extern __shared__ float dr_sm[];                          // k[DR_TB][dk4], q[DR_TB][dk4], then (DK == 0) the state columns
+    extern __shared__ float dr_sm[];                          // k[DR_TB][dk4], q[DR_TB][dk4], bd[DR_TB][2], then (DK == 0) the state columns
+    constexpr int DKP = DK > 0 ? DK / SPLIT : 1;
+    constexpr int COLS = DR_THREADS / SPLIT;
     const int dk4 = (dk + 3) & ~3;
     float* skq = dr_sm;
+    float* sbd = dr_sm + 2 * DR_TB * dk4;
     const int h = blockIdx.x, g = h / (H / G);
-    const int j = blockIdx.y * DR_THREADS + threadIdx.x;
+    const int part = threadIdx.x % SPLIT;
+    const int j = blockIdx.y * COLS + threadIdx.x / SPLIT;
     const bool live = j < dv;
     const int jj = live ? j : dv - 1;                       // idle threads shadow the last column and never store
-    float S[DK > 0 ? DK : 1];
-    float* Ss = dr_sm + 2 * DR_TB * dk4 + threadIdx.x;       // generic: S[i] at Ss[i * DR_THREADS]
-    float* sp = state + ((int64_t)h * dk) * dv + jj;
+    float S[DKP];
+    float* Ss = sbd + 2 * DR_TB + threadIdx.x;               // generic: S[i] at Ss[i * DR_THREADS]
+    float* sp = state + ((int64_t)h * dk + part * DKP) * dv + jj;
     if (DK > 0) {
 #pragma unroll
-        for (int i = 0; i < DK; i++) S[i] = sp[(int64_t)i * dv];
+        for (int i = 0; i < DKP; i++) S[i] = sp[(int64_t)i * dv];
     } else {
         for (int i = 0; i < dk4; i++) Ss[i * DR_THREADS] = i < dk ? sp[(int64_t)i * dv] : 0.0f;
     }
@@ -227,23 +233,32 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const float* __r
             skq[tt * dk4 + i] = i < dk ? k[src] : 0.0f;
             skq[(DR_TB + tt) * dk4 + i] = i < dk ? q[src] : 0.0f;
         }
+        for (int idx = threadIdx.x; idx < nt * 2; idx += DR_THREADS) sbd[idx] = bd[((int64_t)(tb + (idx >> 1)) * H + h) * 2 + (idx & 1)];
+        float vv[DR_TB];
+#pragma unroll
+        for (int tt = 0; tt < DR_TB; tt++) vv[tt] = tt < nt ? v[((int64_t)(tb + tt) * H + h) * dv + jj] : 0.0f;
         __syncthreads();
+#pragma unroll 1
         for (int tt = 0; tt < nt; tt++) {
             const int t = tb + tt;
-            const float* kt = skq + tt * dk4;
-            const float* qt = skq + (DR_TB + tt) * dk4;
-            const float beta = bd[((int64_t)t * H + h) * 2], dec = bd[((int64_t)t * H + h) * 2 + 1];
-            const float vj = v[((int64_t)t * H + h) * dv + jj];
+            const float* kt = skq + tt * dk4 + part * DKP;
+            const float* qt = skq + (DR_TB + tt) * dk4 + part * DKP;
+            const float beta = sbd[tt * 2], dec = sbd[tt * 2 + 1];
+            float vj = vv[0];
+#pragma unroll
+            for (int x = 1; x < DR_TB; x++) vj = tt == x ? vv[x] : vj;
             float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f, o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
             if (DK > 0) {
 #pragma unroll
-                for (int i = 0; i < DK; i += 4) {
+                for (int i = 0; i < DKP; i += 4) {
                     const float4 kv = *(const float4*)(kt + i);
                     a0 = fmaf(S[i], kv.x, a0); a1 = fmaf(S[i + 1], kv.y, a1); a2 = fmaf(S[i + 2], kv.z, a2); a3 = fmaf(S[i + 3], kv.w, a3);
                 }
-                const float u = beta * (vj - dec * ((a0 + a1) + (a2 + a3)));
+                float acc = (a0 + a1) + (a2 + a3);
+                if (SPLIT == 2) acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+                const float u = beta * (vj - dec * acc);
 #pragma unroll
-                for (int i = 0; i < DK; i += 4) {
+                for (int i = 0; i < DKP; i += 4) {
                     const float4 kv = *(const float4*)(kt + i);
                     const float4 qv = *(const float4*)(qt + i);
                     S[i] = fmaf(kv.x, u, dec * S[i]); S[i + 1] = fmaf(kv.y, u, dec * S[i + 1]); S[i + 2] = fmaf(kv.z, u, dec * S[i + 2]); S[i + 3] = fmaf(kv.w, u, dec * S[i + 3]);
@@ -265,13 +280,15 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const float* __r
                     o0 = fmaf(s0, qv.x, o0); o1 = fmaf(s1, qv.y, o1); o2 = fmaf(s2, qv.z, o2); o3 = fmaf(s3, qv.w, o3);
                 }
             }
-            if (live) o[((int64_t)t * H + h) * dv + j] = (o0 + o1) + (o2 + o3);
+            float outv = (o0 + o1) + (o2 + o3);
+            if (SPLIT == 2) outv += __shfl_xor_sync(0xffffffffu, outv, 1);
+            if (live && part == 0) o[((int64_t)t * H + h) * dv + j] = outv;
         }
     }
     if (live) {
         if (DK > 0) {
 #pragma unroll
-            for (int i = 0; i < DK; i++) sp[(int64_t)i * dv] = S[i];
+            for (int i = 0; i < DKP; i++) sp[(int64_t)i * dv] = S[i];
         } else {
             for (int i = 0; i < dk; i++) sp[(int64_t)i * dv] = Ss[i * DR_THREADS];
         }
@@ -301,18 +318,19 @@ extern "C" CC_API int cc_gated_delta_rule(cc_device* dev, const cc_view* q, cons
     if (rc) return rc;
     delta_gates_kernel<<<(unsigned)((T * H + 255) / 256), 256, 0, dev->stream>>>(fptr(a), fptr(b), fptr(a_log), fptr(dt_bias), (float*)bdp, T * H, H);
     dev->launches++;
-    dim3 grid((unsigned)H, (unsigned)((dv + DR_THREADS - 1) / DR_THREADS));
+    const int cols = dk == 128 ? DR_THREADS / 2 : DR_THREADS;
+    dim3 grid((unsigned)H, (unsigned)((dv + cols - 1) / cols));
 #define DR_ARGS fptr(q), fptr(k), fptr(v), (const float*)bdp, fptr(state), (float*)o->base, (int)T, H, G, dk, dv
     const int dk4 = (dk + 3) & ~3;
-    const size_t stage = (size_t)2 * DR_TB * dk4 * 4;
-    if (dk == 32) delta_rule_kernel<32><<<grid, DR_THREADS, stage, dev->stream>>>(DR_ARGS);
-    else if (dk == 64) delta_rule_kernel<64><<<grid, DR_THREADS, stage, dev->stream>>>(DR_ARGS);
-    else if (dk == 128) delta_rule_kernel<128><<<grid, DR_THREADS, stage, dev->stream>>>(DR_ARGS);
+    const size_t stage = ((size_t)2 * DR_TB * dk4 + 2 * DR_TB) * 4;
+    if (dk == 32) delta_rule_kernel<32, 1><<<grid, DR_THREADS, stage, dev->stream>>>(DR_ARGS);
+    else if (dk == 64) delta_rule_kernel<64, 1><<<grid, DR_THREADS, stage, dev->stream>>>(DR_ARGS);
+    else if (dk == 128) delta_rule_kernel<128, 2><<<grid, DR_THREADS, stage, dev->stream>>>(DR_ARGS);
     else {
         const size_t smem = stage + (size_t)dk4 * DR_THREADS * 4;
         if (smem > 200 * 1024) { cc_pool_free(dev, bdp, cls); return cc_fail(dev, CC_ERR_UNSUPPORTED, "gated_delta_rule: dk=%d is too large", dk); }
-        if (smem > 48 * 1024) CC_CUDA(dev, cudaFuncSetAttribute(delta_rule_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        delta_rule_kernel<0><<<grid, DR_THREADS, smem, dev->stream>>>(DR_ARGS);
+        if (smem > 48 * 1024) CC_CUDA(dev, cudaFuncSetAttribute(delta_rule_kernel<0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        delta_rule_kernel<0, 1><<<grid, DR_THREADS, smem, dev->stream>>>(DR_ARGS);
     }
 #undef DR_ARGS
     cc_pool_free(dev, bdp, cls);            // stream-ordered pool: the next user of this block runs after the kernels above
@@ -466,6 +484,30 @@ __global__ void wa_softmax_kernel(float* __restrict__ S, WaGeom g) {
     const float inv = 1.0f / sum;
     for (int c = lane; c < n; c += 32) Sr[c] *= inv;
 }
+// few rows (decoding): one CTA per row = (query, head); the row's probabilities go to shared memory, thread d owns output column d and
+// adds the keys in ascending order -- the same order as the tile kernel below, so both give the same bits
+__global__ void __launch_bounds__(128) wa_values_row_kernel(const float* __restrict__ S, const float* __restrict__ vring, float* __restrict__ out, WaGeom g) {
+    extern __shared__ float wr_sm[];
+    const int64_t row = blockIdx.x;
+    const int t = (int)(row / g.H), h = (int)(row % g.H), kvh = h / g.R;
+    const int64_t i = g.pos0 + t, lo = wa_lo(g, i);
+    const int n = (int)(i - lo + 1);
+    for (int c = threadIdx.x; c < n; c += 128) wr_sm[c] = S[row * g.cap + c];
+    __syncthreads();
+    const int r0 = (int)(lo % g.ring);
+    const int n1 = min(n, g.ring - r0);                      // rows r0 .. of the ring, then (wrapped) rows 0 ..
+    const int64_t rs = (int64_t)g.G * g.dv;
+    for (int d = threadIdx.x; d < g.dv; d += 128) {
+        const float* v1 = vring + ((int64_t)r0 * g.G + kvh) * g.dv + d;
+        const float* v2 = vring + (int64_t)kvh * g.dv + d;
+        float acc = 0.0f;
+#pragma unroll 8
+        for (int c = 0; c < n1; c++) acc = fmaf(wr_sm[c], v1[c * rs], acc);
+#pragma unroll 8
+        for (int c = n1; c < n; c++) acc = fmaf(wr_sm[c], v2[(c - n1) * rs], acc);
+        out[row * g.dv + d] = acc;
+    }
+}
 // grid (dv tiles, query tiles, G)
 __global__ void __launch_bounds__(WA_THREADS) wa_values_kernel(const float* __restrict__ S, const float* __restrict__ vring, float* __restrict__ out, WaGeom g) {
     __shared__ float sp[WA_K][WA_TILE + 4];       // [key][row]
@@ -573,8 +615,14 @@ extern "C" CC_API int cc_window_attention(cc_device* dev, const cc_view* q, cons
     dev->launches++;
     wa_softmax_kernel<<<(unsigned)((T * H + 7) / 8), 256, 0, dev->stream>>>((float*)Sp, g);
     dev->launches++;
-    dim3 g3((unsigned)((dv + WA_TILE - 1) / WA_TILE), (unsigned)q_tiles, (unsigned)G);
-    wa_values_kernel<<<g3, WA_THREADS, 0, dev->stream>>>((const float*)Sp, fptr(vring), (float*)o->base, g);
+    if (T * H <= 64 && (size_t)maxn * 4 <= 160 * 1024) {
+        const size_t smem = (size_t)maxn * 4;
+        if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(wa_values_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) { cc_pool_free(dev, Sp, cls); return cc_fail(dev, CC_ERR_CUDA, "window_attention: %s", cudaGetErrorString(e)); } }
+        wa_values_row_kernel<<<(unsigned)(T * H), 128, smem, dev->stream>>>((const float*)Sp, fptr(vring), (float*)o->base, g);
+    } else {
+        dim3 g3((unsigned)((dv + WA_TILE - 1) / WA_TILE), (unsigned)q_tiles, (unsigned)G);
+        wa_values_kernel<<<g3, WA_THREADS, 0, dev->stream>>>((const float*)Sp, fptr(vring), (float*)o->base, g);
+    }
     cc_pool_free(dev, Sp, cls);
     CC_LAUNCH_CHECK(dev);
     return CC_OK;
