@@ -130,6 +130,8 @@ extern "C" CC_API int cc_moe_route(cc_device* dev, const cc_view* x, const cc_vi
 }
 
 // ---- experts ---------------------------------------------------------------------------------------------------------------------------
+// an id outside [0, E) (only possible with a caller-made table) is clamped, never used as an address
+__device__ __forceinline__ int moe_clamp(int e, int E) { return e < 0 ? 0 : e >= E ? E - 1 : e; }
 __device__ __forceinline__ float moe_w(const float* w, int64_t i) { return w[i]; }
 __device__ __forceinline__ float moe_w(const uint16_t* w, int64_t i) { return __uint_as_float((unsigned)w[i] << 16); }
 template <class WT> __device__ __forceinline__ float moe_round(float v);
@@ -143,10 +145,10 @@ __device__ __forceinline__ float moe_act(float z, int act) {
 // grid (T * top, ceil(ff / 8)), 256 threads: the CTA stages x[t] (rounded for BF16 weights); a warp owns one hidden row of the slot's expert
 template <class WT>
 __global__ void __launch_bounds__(256) moe_gate_up_kernel(const float* __restrict__ x, const int* __restrict__ ids, const WT* __restrict__ wg, const WT* __restrict__ wu,
-                                                          float* __restrict__ hid, int D, int ff, int top, int act) {
+                                                          float* __restrict__ hid, int D, int ff, int top, int act, int E) {
     extern __shared__ float mg_sm[];
     const int ts = blockIdx.x, t = ts / top;
-    const int e = ids[ts];
+    const int e = moe_clamp(ids[ts], E);
     for (int d = threadIdx.x; d < D; d += 256) mg_sm[d] = moe_round<WT>(x[(int64_t)t * D + d]);
     __syncthreads();
     const int r = blockIdx.y * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -160,7 +162,7 @@ __global__ void __launch_bounds__(256) moe_gate_up_kernel(const float* __restric
 // grid (T, ceil(D / 8)), 256 threads: the CTA stages the token's top hidden rows; a warp owns one output coordinate and adds the slots in order
 template <class WT>
 __global__ void __launch_bounds__(256) moe_down_kernel(const float* __restrict__ hid, const int* __restrict__ ids, const float* __restrict__ wts, const WT* __restrict__ wd,
-                                                       float* __restrict__ out, int D, int ff, int top) {
+                                                       float* __restrict__ out, int D, int ff, int top, int E) {
     extern __shared__ float md_sm[];
     const int t = blockIdx.x;
     for (int i = threadIdx.x; i < top * ff; i += 256) md_sm[i] = moe_round<WT>(hid[(int64_t)t * top * ff + i]);
@@ -169,7 +171,7 @@ __global__ void __launch_bounds__(256) moe_down_kernel(const float* __restrict__
     if (d >= D) return;
     float acc = 0.0f;
     for (int s = 0; s < top; s++) {
-        const int e = ids[(int64_t)t * top + s];
+        const int e = moe_clamp(ids[(int64_t)t * top + s], E);
         const int64_t base = ((int64_t)e * D + d) * ff;
         float p = 0.0f;
         for (int f = lane; f < ff; f += 32) p = fmaf(moe_w(wd, base + f), md_sm[s * ff + f], p);
@@ -181,14 +183,14 @@ __global__ void __launch_bounds__(256) moe_down_kernel(const float* __restrict__
 
 template <class WT>
 static int moe_launch(cc_device* dev, const float* x, const int* ids, const float* wts, const void* wg, const void* wu, const void* wd, float* hid, float* out, int64_t T,
-                      int D, int ff, int top, int act) {
+                      int D, int ff, int top, int act, int E) {
     const size_t s1 = (size_t)D * 4, s2 = (size_t)top * ff * 4;
     if (s1 > 200 * 1024 || s2 > 200 * 1024) return cc_fail(dev, CC_ERR_UNSUPPORTED, "moe_experts: row does not fit shared memory");
     if (s1 > 48 * 1024) CC_CUDA(dev, cudaFuncSetAttribute(moe_gate_up_kernel<WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s1));
     if (s2 > 48 * 1024) CC_CUDA(dev, cudaFuncSetAttribute(moe_down_kernel<WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s2));
-    moe_gate_up_kernel<WT><<<dim3((unsigned)(T * top), (unsigned)((ff + 7) / 8)), 256, s1, dev->stream>>>(x, ids, (const WT*)wg, (const WT*)wu, hid, D, ff, top, act);
+    moe_gate_up_kernel<WT><<<dim3((unsigned)(T * top), (unsigned)((ff + 7) / 8)), 256, s1, dev->stream>>>(x, ids, (const WT*)wg, (const WT*)wu, hid, D, ff, top, act, E);
     CC_LAUNCH_CHECK(dev);
-    moe_down_kernel<WT><<<dim3((unsigned)T, (unsigned)((D + 7) / 8)), 256, s2, dev->stream>>>(hid, ids, wts, (const WT*)wd, out, D, ff, top);
+    moe_down_kernel<WT><<<dim3((unsigned)T, (unsigned)((D + 7) / 8)), 256, s2, dev->stream>>>(hid, ids, wts, (const WT*)wd, out, D, ff, top, E);
     CC_LAUNCH_CHECK(dev);
     return CC_OK;
 }
@@ -208,7 +210,7 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ 
     int* off = ms_sm + E;
     for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
     __syncthreads();
-    for (int i = threadIdx.x; i < n; i += blockDim.x) pos[i] = atomicAdd(&cnt[ids[i]], 1);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) pos[i] = atomicAdd(&cnt[moe_clamp(ids[i], E)], 1);
     __syncthreads();
     if (threadIdx.x == 0) {
         int o = 0, nt = 0;
@@ -223,7 +225,7 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ 
         table[0] = nt;
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < n; i += blockDim.x) pos[i] += off[ids[i]];
+    for (int i = threadIdx.x; i < n; i += blockDim.x) pos[i] += off[moe_clamp(ids[i], E)];
 }
 // xs[pos[i]][:] = bf16(x[i / top][:]) ; one warp per entry
 __global__ void moe_gather_bf16_kernel(const float* __restrict__ x, const int* __restrict__ pos, __nv_bfloat16* __restrict__ xs, int n, int top, int D) {
@@ -313,8 +315,8 @@ extern "C" CC_API int cc_moe_experts(cc_device* dev, const cc_view* x, const cc_
     const float* xp = (const float*)x->buf->plane[0];
     const int* ip = (const int*)ids->buf->plane[0];
     const float* wp = (const float*)weights->buf->plane[0];
-    if (wt == CC_F32) rc = moe_launch<float>(dev, xp, ip, wp, w_gate->buf->plane[0], w_up->buf->plane[0], w_down->buf->plane[0], (float*)hid, (float*)o->base, T, (int)D, ff, (int)top, act);
-    else rc = moe_launch<uint16_t>(dev, xp, ip, wp, w_gate->buf->plane[0], w_up->buf->plane[0], w_down->buf->plane[0], (float*)hid, (float*)o->base, T, (int)D, ff, (int)top, act);
+    if (wt == CC_F32) rc = moe_launch<float>(dev, xp, ip, wp, w_gate->buf->plane[0], w_up->buf->plane[0], w_down->buf->plane[0], (float*)hid, (float*)o->base, T, (int)D, ff, (int)top, act, n_experts);
+    else rc = moe_launch<uint16_t>(dev, xp, ip, wp, w_gate->buf->plane[0], w_up->buf->plane[0], w_down->buf->plane[0], (float*)hid, (float*)o->base, T, (int)D, ff, (int)top, act, n_experts);
     cc_pool_free(dev, hid, cls);
     return rc;
 }

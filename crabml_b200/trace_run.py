@@ -51,6 +51,8 @@ def main(argv=None):
             if rid not in slots:
                 slots[rid] = model.open()
             want = list(e.get("want", []))
+            if not e["tokens"]:
+                continue
             lg = model.step(slots[rid], e["tokens"], want)
             if want:
                 rows.append(lg)
