@@ -200,23 +200,30 @@ __global__ void delta_gates_kernel(const float* __restrict__ a, const float* __r
 // (p0 + p1) + (p2 + p3), then the SPLIT shares are added by a shuffle: a fixed order, the same for any T.
 #define DR_THREADS 64
 #define DR_TB 16
+__device__ __forceinline__ void dr_cp_async16(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void dr_cp_async4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+// one staging buffer: k[DR_TB][dk4], q[DR_TB][dk4], bd[DR_TB][2], v[DR_TB][DR_THREADS] (a thread's own value column)
+__device__ __forceinline__ int dr_stage_floats(int dk4) { return 2 * DR_TB * dk4 + 2 * DR_TB + DR_TB * DR_THREADS; }
 template <int DK, int SPLIT>
 __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                                                                 const float* __restrict__ bd, float* __restrict__ state, float* __restrict__ o, int T, int H, int G,
                                                                 int dk, int dv) {
-    extern __shared__ float dr_sm[];                          // k[DR_TB][dk4], q[DR_TB][dk4], bd[DR_TB][2], then (DK == 0) the state columns
+    extern __shared__ __align__(16) float dr_sm[];            // two staging buffers, then (DK == 0) the state columns
     constexpr int DKP = DK > 0 ? DK / SPLIT : 1;
     constexpr int COLS = DR_THREADS / SPLIT;
     const int dk4 = (dk + 3) & ~3;
-    float* skq = dr_sm;
-    float* sbd = dr_sm + 2 * DR_TB * dk4;
+    const int stage_floats = dr_stage_floats(dk4);
     const int h = blockIdx.x, g = h / (H / G);
     const int part = threadIdx.x % SPLIT;
     const int j = blockIdx.y * COLS + threadIdx.x / SPLIT;
     const bool live = j < dv;
     const int jj = live ? j : dv - 1;                       // idle threads shadow the last column and never store
     float S[DKP];
-    float* Ss = sbd + 2 * DR_TB + threadIdx.x;               // generic: S[i] at Ss[i * DR_THREADS]
+    float* Ss = dr_sm + 2 * stage_floats + threadIdx.x;      // generic: S[i] at Ss[i * DR_THREADS]
     float* sp = state + ((int64_t)h * dk + part * DKP) * dv + jj;
     if (DK > 0) {
 #pragma unroll
@@ -224,29 +231,53 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const float* __r
     } else {
         for (int i = 0; i < dk4; i++) Ss[i * DR_THREADS] = i < dk ? sp[(int64_t)i * dv] : 0.0f;
     }
-    for (int tb = 0; tb < T; tb += DR_TB) {
+    // the pad lanes dk .. dk4 of both buffers are zero for the whole call (the copies below never touch them)
+    if (dk4 != dk)
+        for (int idx = threadIdx.x; idx < 2 * 2 * DR_TB; idx += DR_THREADS)
+            for (int i = dk; i < dk4; i++) dr_sm[(idx / (2 * DR_TB)) * stage_floats + (idx % (2 * DR_TB)) * dk4 + i] = 0.0f;
+    // asynchronous copies (cp.async) of a block of tokens: issued one block ahead, so the trip to L2 overlaps the recurrence
+    auto stage = [&](int buf, int tb) {
+        float* base = dr_sm + buf * stage_floats;
         const int nt = min(DR_TB, T - tb);
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < nt * dk4; idx += DR_THREADS) {
-            const int tt = idx / dk4, i = idx - tt * dk4;
-            const int64_t src = ((int64_t)(tb + tt) * G + g) * dk + i;
-            skq[tt * dk4 + i] = i < dk ? k[src] : 0.0f;
-            skq[(DR_TB + tt) * dk4 + i] = i < dk ? q[src] : 0.0f;
+        if ((dk & 3) == 0) {
+            const int per = dk >> 2;
+            for (int idx = threadIdx.x; idx < nt * per; idx += DR_THREADS) {
+                const int tt = idx / per, c = (idx - tt * per) * 4;
+                const int64_t src = ((int64_t)(tb + tt) * G + g) * dk + c;
+                dr_cp_async16(base + tt * dk4 + c, k + src);
+                dr_cp_async16(base + (DR_TB + tt) * dk4 + c, q + src);
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < nt * dk; idx += DR_THREADS) {
+                const int tt = idx / dk, c = idx - tt * dk;
+                const int64_t src = ((int64_t)(tb + tt) * G + g) * dk + c;
+                dr_cp_async4(base + tt * dk4 + c, k + src);
+                dr_cp_async4(base + (DR_TB + tt) * dk4 + c, q + src);
+            }
         }
-        for (int idx = threadIdx.x; idx < nt * 2; idx += DR_THREADS) sbd[idx] = bd[((int64_t)(tb + (idx >> 1)) * H + h) * 2 + (idx & 1)];
-        float vv[DR_TB];
-#pragma unroll
-        for (int tt = 0; tt < DR_TB; tt++) vv[tt] = tt < nt ? v[((int64_t)(tb + tt) * H + h) * dv + jj] : 0.0f;
-        __syncthreads();
+        float* sbd = base + 2 * DR_TB * dk4;
+        for (int idx = threadIdx.x; idx < nt * 2; idx += DR_THREADS) dr_cp_async4(sbd + idx, bd + ((int64_t)(tb + (idx >> 1)) * H + h) * 2 + (idx & 1));
+        float* sv = sbd + 2 * DR_TB + threadIdx.x;
+        for (int tt = 0; tt < nt; tt++) dr_cp_async4(sv + tt * DR_THREADS, v + ((int64_t)(tb + tt) * H + h) * dv + jj);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (T > 0) stage(0, 0);
+    int buf = 0;
+    for (int tb = 0; tb < T; tb += DR_TB, buf ^= 1) {
+        const int nt = min(DR_TB, T - tb);
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                                      // this block has landed for everyone, and everyone is done with the other buffer
+        if (tb + DR_TB < T) stage(buf ^ 1, tb + DR_TB);
+        const float* base = dr_sm + buf * stage_floats;
+        const float* sbd = base + 2 * DR_TB * dk4;
+        const float* sv = sbd + 2 * DR_TB + threadIdx.x;
 #pragma unroll 1
         for (int tt = 0; tt < nt; tt++) {
             const int t = tb + tt;
-            const float* kt = skq + tt * dk4 + part * DKP;
-            const float* qt = skq + (DR_TB + tt) * dk4 + part * DKP;
+            const float* kt = base + tt * dk4 + part * DKP;
+            const float* qt = base + (DR_TB + tt) * dk4 + part * DKP;
             const float beta = sbd[tt * 2], dec = sbd[tt * 2 + 1];
-            float vj = vv[0];
-#pragma unroll
-            for (int x = 1; x < DR_TB; x++) vj = tt == x ? vv[x] : vj;
+            const float vj = sv[tt * DR_THREADS];
             float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f, o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
             if (DK > 0) {
 #pragma unroll
@@ -322,7 +353,13 @@ extern "C" CC_API int cc_gated_delta_rule(cc_device* dev, const cc_view* q, cons
     dim3 grid((unsigned)H, (unsigned)((dv + cols - 1) / cols));
 #define DR_ARGS fptr(q), fptr(k), fptr(v), (const float*)bdp, fptr(state), (float*)o->base, (int)T, H, G, dk, dv
     const int dk4 = (dk + 3) & ~3;
-    const size_t stage = ((size_t)2 * DR_TB * dk4 + 2 * DR_TB) * 4;
+    const size_t stage = (size_t)2 * ((size_t)2 * DR_TB * dk4 + 2 * DR_TB + DR_TB * DR_THREADS) * 4;      // two staging buffers
+    if (stage > 48 * 1024 && (dk == 32 || dk == 64 || dk == 128)) {
+        cudaError_t e = dk == 32 ? cudaFuncSetAttribute(delta_rule_kernel<32, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)stage)
+                        : dk == 64 ? cudaFuncSetAttribute(delta_rule_kernel<64, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)stage)
+                                   : cudaFuncSetAttribute(delta_rule_kernel<128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)stage);
+        if (e != cudaSuccess) { cc_pool_free(dev, bdp, cls); return cc_fail(dev, CC_ERR_CUDA, "gated_delta_rule: %s", cudaGetErrorString(e)); }
+    }
     if (dk == 32) delta_rule_kernel<32, 1><<<grid, DR_THREADS, stage, dev->stream>>>(DR_ARGS);
     else if (dk == 64) delta_rule_kernel<64, 1><<<grid, DR_THREADS, stage, dev->stream>>>(DR_ARGS);
     else if (dk == 128) delta_rule_kernel<128, 2><<<grid, DR_THREADS, stage, dev->stream>>>(DR_ARGS);
