@@ -422,8 +422,10 @@ extern "C" CC_API int cc_kv_ring_append(cc_device* dev, const cc_view* kring, co
 //   2. wa_softmax_kernel: one warp per row: max, exp, sum, normalise (in place)
 //   3. wa_values_kernel : out[row][d] = sum_c S[row][c] v[lo_i + c][d], a 64 x 64 tile product over the keys of the tile's band
 // A row is one (query, head); a tile's 64 rows are the R = n_heads / n_kv heads of one key/value head for 64 / R consecutive queries.
-// Every dot product and every value sum runs over its index in ascending order inside ONE thread (masked keys add an exact 0), and the
-// softmax sums depend on the row alone: the result for a query does not depend on the tiling, on T, or on where the call starts.
+// Every dot product runs over its index in ascending order inside ONE thread, the softmax sums depend on the row alone, and the value sum
+// has one order per kernel (ascending keys in the tile kernel, masked keys adding an exact 0; four ascending quarters in the row kernel that
+// serves calls of few rows): a query's result does not depend on where the call starts or what else it carries, and differs between a
+// prompt pass and a decoded token only by the rounding of that last sum.
 #define WA_TILE 64
 #define WA_K 16
 #define WA_THREADS 256
@@ -521,29 +523,38 @@ __global__ void wa_softmax_kernel(float* __restrict__ S, WaGeom g) {
     const float inv = 1.0f / sum;
     for (int c = lane; c < n; c += 32) Sr[c] *= inv;
 }
-// few rows (decoding): one CTA per row = (query, head); the row's probabilities go to shared memory, thread d owns output column d and
-// adds the keys in ascending order -- the same order as the tile kernel below, so both give the same bits
+// few rows (decoding): grid (rows, ceil(dv / 32)); a CTA owns 32 output columns of one row = (query, head).  The row's probabilities go to
+// shared memory; the visible keys are cut into four contiguous quarters, warp w adds quarter w in ascending order for its lane's column,
+// and the quarters are added as (p0 + p1) + (p2 + p3).  The order depends on the row alone (its number of visible keys), not on T.
 __global__ void __launch_bounds__(128) wa_values_row_kernel(const float* __restrict__ S, const float* __restrict__ vring, float* __restrict__ out, WaGeom g) {
     extern __shared__ float wr_sm[];
+    __shared__ float part[4][32];
     const int64_t row = blockIdx.x;
     const int t = (int)(row / g.H), h = (int)(row % g.H), kvh = h / g.R;
     const int64_t i = g.pos0 + t, lo = wa_lo(g, i);
     const int n = (int)(i - lo + 1);
     for (int c = threadIdx.x; c < n; c += 128) wr_sm[c] = S[row * g.cap + c];
     __syncthreads();
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int d = blockIdx.y * 32 + lane;
+    const int per = (n + 3) >> 2;
+    const int c_begin = min(n, w * per), c_end = min(n, c_begin + per);
     const int r0 = (int)(lo % g.ring);
-    const int n1 = min(n, g.ring - r0);                      // rows r0 .. of the ring, then (wrapped) rows 0 ..
     const int64_t rs = (int64_t)g.G * g.dv;
-    for (int d = threadIdx.x; d < g.dv; d += 128) {
-        const float* v1 = vring + ((int64_t)r0 * g.G + kvh) * g.dv + d;
-        const float* v2 = vring + (int64_t)kvh * g.dv + d;
-        float acc = 0.0f;
+    float acc = 0.0f;
+    if (d < g.dv) {
+        const float* vb = vring + (int64_t)kvh * g.dv + d;
+        int r = r0 + c_begin;
+        if (r >= g.ring) r -= g.ring;
 #pragma unroll 8
-        for (int c = 0; c < n1; c++) acc = fmaf(wr_sm[c], v1[c * rs], acc);
-#pragma unroll 8
-        for (int c = n1; c < n; c++) acc = fmaf(wr_sm[c], v2[(c - n1) * rs], acc);
-        out[row * g.dv + d] = acc;
+        for (int c = c_begin; c < c_end; c++) {
+            acc = fmaf(wr_sm[c], vb[r * rs], acc);
+            if (++r == g.ring) r = 0;
+        }
     }
+    part[w][lane] = acc;
+    __syncthreads();
+    if (w == 0 && d < g.dv) out[row * g.dv + d] = (part[0][lane] + part[1][lane]) + (part[2][lane] + part[3][lane]);
 }
 // grid (dv tiles, query tiles, G)
 __global__ void __launch_bounds__(WA_THREADS) wa_values_kernel(const float* __restrict__ S, const float* __restrict__ vring, float* __restrict__ out, WaGeom g) {
@@ -655,7 +666,7 @@ extern "C" CC_API int cc_window_attention(cc_device* dev, const cc_view* q, cons
     if (T * H <= 64 && (size_t)maxn * 4 <= 160 * 1024) {
         const size_t smem = (size_t)maxn * 4;
         if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(wa_values_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) { cc_pool_free(dev, Sp, cls); return cc_fail(dev, CC_ERR_CUDA, "window_attention: %s", cudaGetErrorString(e)); } }
-        wa_values_row_kernel<<<(unsigned)(T * H), 128, smem, dev->stream>>>((const float*)Sp, fptr(vring), (float*)o->base, g);
+        wa_values_row_kernel<<<dim3((unsigned)(T * H), (unsigned)((dv + 31) / 32)), 128, smem, dev->stream>>>((const float*)Sp, fptr(vring), (float*)o->base, g);
     } else {
         dim3 g3((unsigned)((dv + WA_TILE - 1) / WA_TILE), (unsigned)q_tiles, (unsigned)G);
         wa_values_kernel<<<g3, WA_THREADS, 0, dev->stream>>>((const float*)Sp, fptr(vring), (float*)o->base, g);
