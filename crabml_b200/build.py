@@ -28,7 +28,7 @@ def needs_build() -> bool:
         return True
     t = os.path.getmtime(LIB)
     deps = sources() + glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(CSRC, "host", "*.hpp")) + \
-        [os.path.join(os.path.dirname(HERE), "include", "crabml_cuda.h"), os.path.abspath(__file__)]
+        glob.glob(os.path.join(os.path.dirname(HERE), "include", "*.h")) + [os.path.abspath(__file__)]
     return any(os.path.getmtime(d) > t for d in deps)
 
 

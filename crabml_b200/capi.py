@@ -19,7 +19,8 @@ CC_MAX_DIMS = 4
 F32, F16, Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q8_1 = 0, 1, 2, 3, 6, 7, 8, 9
 Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, Q8_K = 10, 11, 12, 13, 14, 15
 I32, BF16 = 26, 30
-ACT_NONE, ACT_SILU, ACT_GELU_TANH = 0, 1, 2
+ACT_NONE, ACT_SILU, ACT_GELU_TANH, ACT_SWISH = 0, 1, 2, 3
+ROUTE_SOFTMAX, ROUTE_SIGMOID = 0, 1
 ROPE_LLAMA, ROPE_NEOX = 0, 1
 
 
@@ -77,6 +78,32 @@ CZR_WEIGHT_FIELDS = ("norm1", "norm2", "q", "k", "v", "o", "q_conv", "k_conv", "
 
 class czr_layer_weights(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in CZR_WEIGHT_FIELDS]
+
+
+class cmr_layer_config(C.Structure):            # include/crabml_meresun.h
+    _fields_ = [(n, C.c_int32) for n in ("heads", "dim", "rot_dim", "vdim", "q_rank", "kv_rank", "window")] + [("scale", C.c_float), ("rot_mag", C.c_float)] + \
+               [(n, C.c_int32) for n in ("ff_kind", "ff", "experts", "top", "groups", "keep_groups")] + [("limit", C.c_float)]
+
+
+class cmr_config(C.Structure):
+    _fields_ = [("n_layers", C.c_int32), ("width", C.c_int32), ("vocab", C.c_int32), ("norm_eps", C.c_float)] + \
+               [(n, C.c_int32) for n in ("norm_groups", "loop_start", "loop_stop", "loop_times", "side_dim", "chunk", "max_seq")]
+
+
+CMR_WEIGHT_FIELDS = ("norm1", "dq", "dq_norm", "uq", "dkv", "dkv_norm", "uk", "uv", "sink", "rot_freq", "o", "rg1", "rg1_b", "rg2", "rg2_b", "up", "down", "act",
+                     "router", "correction", "e_gate", "e_up", "e_down", "side_table", "side_gate", "side_proj", "side_norm")
+
+
+class cmr_layer_weights(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in CMR_WEIGHT_FIELDS]
+
+
+class cc_route_params(C.Structure):              # include/crabml_seqops.h
+    _fields_ = [(n, C.c_int32) for n in ("score", "top", "n_groups", "keep_groups", "group_top", "renormalise")] + [("renorm_eps", C.c_float)]
+
+
+class cc_glu_params(C.Structure):
+    _fields_ = [("act", C.c_int32), ("alpha", C.c_float), ("limit", C.c_float), ("up_shift", C.c_float)]
 
 
 _lib = None
@@ -180,6 +207,26 @@ def load_library(build_if_missing: bool = True):
         "cc_window_attention": (i32, [vp, pv, pv, f32, pv, pv, i64, i32, i32, i32, i32, i32, f32, pv, pv, pp]),
         "cc_moe_route": (i32, [vp, pv, pv, pv, i32, i32, i32, i32, pp, pp]),
         "cc_moe_experts": (i32, [vp, pv, pv, pv, pv, pv, pv, i32, i32, i32, pp]),
+        "cc_group_rms_norm": (i32, [vp, pv, pv, pv, i32, f32]),
+        "cc_poly_norm": (i32, [vp, pv, pv, f32]),
+        "cc_gated_sum": (i32, [vp, pv, i32, pv, pv, pv, pv, pv, pv]),
+        "cc_window_attention_sink": (i32, [vp, pv, pv, f32, pv, pv, i64, i32, i32, i32, i32, i32, f32, pv, pv, pv, pp]),
+        "cc_rope_pairs": (i32, [vp, pv, i32, i32, i32, pv, f32, i64]),
+        "cc_latent_ring_append": (i32, [vp, pv, pv, pv, f32, i32, pv, f32, i64]),
+        "cc_head_absorb": (i32, [vp, pv, pv, i32, i32, i32, pp]),
+        "cc_head_expand": (i32, [vp, pv, pv, i32, i32, pp]),
+        "cc_moe_route_ex": (i32, [vp, pv, pv, pv, C.POINTER(cc_route_params), pp, pp]),
+        "cc_moe_experts_glu": (i32, [vp, pv, pv, pv, pv, pv, pv, i32, i32, C.POINTER(cc_glu_params), pp]),
+        "csr_runner_destroy": (None, [vp]),
+        "csr_runner_last_error": (C.c_char_p, [vp]),
+        "csr_last_create_error": (C.c_char_p, []),
+        "csr_seq_open": (i32, [vp, C.POINTER(i32)]),
+        "csr_seq_close": (i32, [vp, i32]),
+        "csr_seq_len": (i64, [vp, i32]),
+        "csr_runner_stats": (i32, [vp, C.POINTER(i64)]),
+        "csr_runner_step": (i32, [vp, i32, C.POINTER(i64), i32, C.POINTER(i32), i32, vp]),
+        "csr_runner_generate_greedy": (i32, [vp, i32, C.POINTER(i64), i32, i32, i64, C.POINTER(i64), C.POINTER(i32)]),
+        "cmr_runner_create": (i32, [vp, C.POINTER(cmr_config), C.POINTER(cmr_layer_config), C.POINTER(cmr_layer_weights), vp, vp, vp, pp]),
         "czr_runner_create": (i32, [vp, C.POINTER(czr_config), C.POINTER(czr_layer_config), C.POINTER(czr_layer_weights), vp, vp, vp, pp]),
         "czr_last_create_error": (C.c_char_p, []),
         "czr_runner_destroy": (None, [vp]),

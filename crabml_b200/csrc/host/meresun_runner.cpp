@@ -1,0 +1,256 @@
+// meresun_runner.cpp -- host driver of the Meresun decoder family over the C ABI (crabml_cuda.h + crabml_seqops.h).  Like the other
+// runners it contains no arithmetic: it owns the weights' handles, says what a sequence holds (one latent cache per layer RUN) and
+// in which order the tensor ops run.  Slots, step and greedy generation are the shared ones of seq_runner.hpp.
+//
+//   run:     h = group_norm(x) ; x += mixer(h) * sigmoid(W_g1 h + b1) + ff(h) * sigmoid(W_g2 h + b2) ; x += token_side(x, token)
+//   mixer:   c_q = norm(W_dq h) ; q = W_uq c_q, rotated part turned ; row [norm(c) | turned r] of W_dkv h into the run's ring ;
+//            q folded through W_uk ; windowed softmax with a sink over the ring's rows ; result through W_uv per head ; W_o
+//   ff:      W_down PolyNorm(W_up h)   or   router -> top experts, weighted sum
+#include <cmath>
+#include <string>
+#include <vector>
+
+#include "../../../include/crabml_meresun.h"
+#include "seq_runner.hpp"
+
+using crabml::CudaTensor;
+using crabml::TensorError;
+
+namespace {
+
+struct Layer {
+    cmr_layer_config c{};
+    CudaTensor norm1, dq, dq_norm, uq, dkv, dkv_norm, uk, uv, sink, rot_freq, o, rg1, rg1_b, rg2, rg2_b, up, down, act, router, correction, e_gate, e_up, e_down, side_table,
+        side_gate, side_proj, side_norm;
+    int64_t ring = 0;            // rows of the latent cache of one run of this layer
+};
+// a run of a layer: looped layers run several times with the same weights, each time on a cache of its own
+struct Run {
+    int layer;
+    bool add_embedding;          // the first layer of a repeated pass: the embedding output joins x before it
+};
+struct State : crabml::SeqState {
+    std::vector<CudaTensor> ring;          // per run: [rows, kv_rank + rot_dim]
+};
+const cc_view* opt(const CudaTensor& t, cc_view& store) {
+    if (!t.valid()) return nullptr;
+    store = t.view();
+    return &store;
+}
+
+struct Runner : csr_runner {
+    cmr_config conf{};
+    std::vector<Layer> layers;
+    std::vector<Run> runs;
+    CudaTensor embed, final_norm, head;
+
+    std::unique_ptr<crabml::SeqState> make_state() override {
+        auto s = std::make_unique<State>();
+        for (const Run& r : runs) {
+            const Layer& L = layers[r.layer];
+            s->ring.push_back(CudaTensor::alloc({L.ring, (int64_t)L.c.kv_rank + L.c.rot_dim}, CC_F32, dev));
+        }
+        return s;
+    }
+    // nothing to clear: a query at position i only reads rows of positions <= i of ITS sequence, all written since the slot was opened
+    void reset_state(crabml::SeqState&) override {}
+
+    CudaTensor norm(const CudaTensor& x, const CudaTensor& w, int groups) {
+        CudaTensor h = CudaTensor::alloc(x.shape(), CC_F32, dev);
+        cc_view hv = h.view(), xv = x.view(), wv = w.view();
+        check(cc_group_rms_norm(dev, &hv, &xv, &wv, groups, conf.norm_eps));
+        return h;
+    }
+
+    CudaTensor mixer(const Layer& L, CudaTensor& ring, const CudaTensor& h, int64_t pos0) {
+        const auto& c = L.c;
+        const int64_t n = h.shape()[0];
+        if (c.window <= 0 && pos0 + n > L.ring) throw TensorError("a sequence of " + std::to_string(pos0 + n) + " tokens does not fit the cache of " + std::to_string(L.ring));
+        cc_view fq{};
+        const cc_view* freq = opt(L.rot_freq, fq);
+        // the cache row of every new token
+        {
+            CudaTensor ckv = L.dkv.matmul_vec(h);
+            cc_view rv = ring.view(), cv = ckv.view(), nw{};
+            check(cc_latent_ring_append(dev, &rv, &cv, opt(L.dkv_norm, nw), conf.norm_eps, c.kv_rank, freq, c.rot_mag, pos0));
+        }
+        // queries through their latent
+        CudaTensor cq = L.dq.matmul_vec(h);
+        cq = norm(cq, L.dq_norm, 1);
+        CudaTensor q = L.uq.matmul_vec(cq);
+        cc_view qv = q.view();
+        if (freq) check(cc_rope_pairs(dev, &qv, c.heads, c.dim + c.rot_dim, c.dim, freq, c.rot_mag, pos0));
+        cc_buf* b = nullptr;
+        cc_view ukv = L.uk.view();
+        check(cc_head_absorb(dev, &qv, &ukv, c.heads, c.dim, c.rot_dim, &b));
+        CudaTensor ql = adopt(b, {n, (int64_t)c.heads * (c.kv_rank + c.rot_dim)});
+        // all heads read the one cached row per position: keys are whole rows, values their first kv_rank columns
+        cc_view qlv = ql.view(), rv = ring.view(), sk{};
+        b = nullptr;
+        check(cc_window_attention_sink(dev, &qlv, nullptr, 0.0f, &rv, nullptr, pos0, c.heads, 1, c.kv_rank + c.rot_dim, c.kv_rank, c.window, c.scale, nullptr, nullptr,
+                                       opt(L.sink, sk), &b));
+        CudaTensor ol = adopt(b, {n, (int64_t)c.heads * c.kv_rank});
+        cc_view olv = ol.view(), uvv = L.uv.view();
+        b = nullptr;
+        check(cc_head_expand(dev, &olv, &uvv, c.heads, c.vdim, &b));
+        CudaTensor o = adopt(b, {n, (int64_t)c.heads * c.vdim});
+        return L.o.matmul_vec(o);
+    }
+
+    CudaTensor feed_forward(const Layer& L, const CudaTensor& h) {
+        const auto& c = L.c;
+        const int64_t n = h.shape()[0];
+        if (c.ff_kind == CMR_FF_DENSE) {
+            CudaTensor z = L.up.matmul_vec(h);
+            cc_view zv = z.view(), av = L.act.view();
+            check(cc_poly_norm(dev, &zv, &av, conf.norm_eps));
+            return L.down.matmul_vec(z);
+        }
+        cc_view hv = h.view(), rw = L.router.view(), cv{};
+        cc_buf *ids = nullptr, *wts = nullptr, *ob = nullptr;
+        const cc_route_params rp = {CC_ROUTE_SIGMOID, c.top, c.groups, c.keep_groups, 2, 1, 1e-20f};
+        check(cc_moe_route_ex(dev, &hv, &rw, opt(L.correction, cv), &rp, &ids, &wts));
+        CudaTensor tid = adopt(ids, {n, c.top}), tw = adopt(wts, {n, c.top});
+        cc_view iv = tid.view(), wv = tw.view(), g = L.e_gate.view(), u = L.e_up.view(), d = L.e_down.view();
+        const cc_glu_params glu = {CC_ACT_SWISH, 1.702f, c.limit, 1.0f};
+        check(cc_moe_experts_glu(dev, &hv, &iv, &wv, &g, &u, &d, c.experts, c.ff, &glu, &ob));
+        return adopt(ob, {n, conf.width});
+    }
+
+    CudaTensor forward_chunk(crabml::SeqState& base, int64_t pos0, const int64_t* tokens, int64_t n, int device_slot) override {
+        State& s = static_cast<State&>(base);
+        auto gather = [&](const CudaTensor& table, int64_t cols) {
+            CudaTensor t = CudaTensor::alloc({n, cols}, CC_F32, dev);
+            if (device_slot >= 0) t.copy_rows_from_slot(table, device_slot);
+            else t.copy_rows_from(table, std::vector<int64_t>(tokens, tokens + n));
+            return t;
+        };
+        CudaTensor x = gather(embed, conf.width);
+        CudaTensor x0;
+        for (const Run& r : runs)
+            if (r.add_embedding) { x0 = x.dup(); break; }
+        for (size_t ri = 0; ri < runs.size(); ri++) {
+            const Layer& L = layers[runs[ri].layer];
+            if (runs[ri].add_embedding) x = std::move(x).add_inplace(x0);
+            {
+                CudaTensor h = norm(x, L.norm1, conf.norm_groups);
+                CudaTensor y = mixer(L, s.ring[ri], h, pos0);
+                CudaTensor g1, f, g2;
+                if (L.rg1.valid()) g1 = L.rg1.matmul_vec(h);
+                if (L.c.ff_kind != CMR_FF_NONE) {
+                    f = feed_forward(L, h);
+                    if (L.rg2.valid()) g2 = L.rg2.matmul_vec(h);
+                }
+                cc_view xv = x.view(), yv = y.view(), g1v{}, b1v{}, fv{}, g2v{}, b2v{};
+                check(cc_gated_sum(dev, &xv, 1, &yv, opt(g1, g1v), opt(L.rg1_b, b1v), opt(f, fv), opt(g2, g2v), opt(L.rg2_b, b2v)));
+            }
+            if (L.side_table.valid()) {
+                CudaTensor g = L.side_gate.matmul_vec(x);
+                CudaTensor e = gather(L.side_table, conf.side_dim);
+                cc_view gv = g.view(), ev = e.view();
+                check(cc_glu_inplace(dev, &gv, &ev, CC_ACT_GELU_TANH));
+                CudaTensor y = L.side_proj.matmul_vec(g);
+                cc_view xv = x.view(), yv = y.view(), nv = L.side_norm.view();
+                check(cc_rms_norm_gain(dev, &xv, &yv, &nv, conf.norm_eps, 1));
+            }
+            x = std::move(x).with_name("run:" + std::to_string(ri) + ":" + std::to_string(pos0));
+        }
+        return x;
+    }
+
+    CudaTensor logits_of(const CudaTensor& x, const std::vector<int64_t>& rows) override {
+        CudaTensor xs = CudaTensor::alloc({(int64_t)rows.size(), conf.width}, CC_F32, dev);
+        xs.copy_rows_from(x, rows);
+        return head.matmul_vec(norm(xs, final_norm, conf.norm_groups));
+    }
+};
+
+}  // namespace
+
+extern "C" CC_API int cmr_runner_create(cc_device* dev, const cmr_config* conf, const cmr_layer_config* lc, const cmr_layer_weights* lw, cc_buf* embed, cc_buf* final_norm,
+                                        cc_buf* head, csr_runner** out) {
+    if (!dev || !conf || !lc || !lw || !embed || !final_norm || !head || !out) return CC_ERR_ARG;
+    Runner* r = new Runner();
+    r->dev = dev;
+    r->conf = *conf;
+    if (r->conf.chunk <= 0) r->conf.chunk = 256;
+    if (r->conf.max_seq <= 0) r->conf.max_seq = 4096;
+    r->width = conf->width; r->vocab = conf->vocab; r->chunk = r->conf.chunk;
+    std::string err;
+    int rc = crabml::seq_guarded(r, &err, [&] {
+        const int64_t D = conf->width;
+        if (conf->n_layers < 1 || D < 1 || conf->vocab < 1) throw TensorError("bad model sizes");
+        if (conf->norm_groups < 1 || D % conf->norm_groups) throw TensorError("the norm's groups do not divide the width");
+        r->embed = CudaTensor::wrap(dev, embed, {conf->vocab, D});
+        r->final_norm = CudaTensor::wrap(dev, final_norm, {D});
+        r->head = CudaTensor::wrap(dev, head, {conf->vocab, D});
+        r->layers.resize(conf->n_layers);
+        for (int i = 0; i < conf->n_layers; i++) {
+            Layer& L = r->layers[i];
+            const cmr_layer_config& c = L.c = lc[i];
+            const cmr_layer_weights& w = lw[i];
+            const std::string at = "layer " + std::to_string(i) + ": ";
+            if (c.heads < 1 || c.dim < 1 || c.rot_dim < 0 || c.vdim < 1 || c.q_rank < 1 || c.kv_rank < 1) throw TensorError(at + "bad head counts / sizes");
+            if (c.heads > 64) throw TensorError(at + "more than 64 heads over one shared cache row are not supported");
+            if (c.vdim > 0 && c.kv_rank + c.rot_dim < c.kv_rank) throw TensorError(at + "bad sizes");
+            auto need = [&](cc_buf* b, const char* name, std::vector<int64_t> shape) {
+                if (!b) throw TensorError(at + "tensor '" + name + "' is missing");
+                return CudaTensor::wrap(dev, b, shape);
+            };
+            auto maybe = [&](cc_buf* b, std::vector<int64_t> shape) { return b ? CudaTensor::wrap(dev, b, shape) : CudaTensor(); };
+            const int64_t qh = c.dim + c.rot_dim, hv = (int64_t)c.heads * c.vdim;
+            L.norm1 = need(w.norm1, "norm1", {D});
+            L.dq = need(w.dq, "mix.dq", {c.q_rank, D}); L.dq_norm = need(w.dq_norm, "mix.dq.norm", {c.q_rank}); L.uq = need(w.uq, "mix.uq", {c.heads * qh, c.q_rank});
+            L.dkv = need(w.dkv, "mix.dkv", {(int64_t)c.kv_rank + c.rot_dim, D}); L.dkv_norm = need(w.dkv_norm, "mix.dkv.norm", {c.kv_rank});
+            L.uk = need(w.uk, "mix.uk", {(int64_t)c.heads * c.dim, c.kv_rank}); L.uv = need(w.uv, "mix.uv", {hv, c.kv_rank});
+            L.o = need(w.o, "mix.o", {D, hv});
+            L.sink = maybe(w.sink, {c.heads});
+            if (w.rot_freq) {
+                const int64_t pairs = cc_tensor_capacity(w.rot_freq);
+                if (2 * pairs > c.rot_dim) throw TensorError(at + "more rotated pairs than the rotated part holds");
+                L.rot_freq = CudaTensor::wrap(dev, w.rot_freq, {pairs});
+            }
+            if (L.uk.dtype() != CC_F32 || L.uv.dtype() != CC_F32) throw TensorError(at + "mix.uk / mix.uv must be F32: they enter the 32-bit scores and sums");
+            L.rg1 = maybe(w.rg1, {D, D}); L.rg1_b = maybe(w.rg1_b, {D}); L.rg2 = maybe(w.rg2, {D, D}); L.rg2_b = maybe(w.rg2_b, {D});
+            if ((L.rg1_b.valid() && !L.rg1.valid()) || (L.rg2_b.valid() && !L.rg2.valid())) throw TensorError(at + "a gate's bias without the gate");
+            if (c.ff_kind == CMR_FF_DENSE) {
+                if (c.ff < 1) throw TensorError(at + "bad feed-forward width");
+                L.up = need(w.up, "mlp.up", {c.ff, D}); L.down = need(w.down, "mlp.down", {D, c.ff}); L.act = need(w.act, "mlp.act", {4});
+            } else if (c.ff_kind == CMR_FF_ROUTED) {
+                if (c.experts < 1 || c.top < 1 || c.top > c.experts || c.ff < 1) throw TensorError(at + "bad router sizes");
+                L.router = need(w.router, "mlp.router", {c.experts, D});
+                L.correction = maybe(w.correction, {c.experts});
+                L.e_gate = need(w.e_gate, "mlp.e*.gate", {(int64_t)c.experts * c.ff, D});
+                L.e_up = need(w.e_up, "mlp.e*.up", {(int64_t)c.experts * c.ff, D});
+                L.e_down = need(w.e_down, "mlp.e*.down", {(int64_t)c.experts * D, c.ff});
+            } else if (c.ff_kind != CMR_FF_NONE) throw TensorError(at + "unknown feed-forward kind");
+            if (conf->side_dim > 0) {
+                L.side_table = need(w.side_table, "side.embed", {conf->vocab, conf->side_dim});
+                L.side_gate = need(w.side_gate, "side.gate", {conf->side_dim, D}); L.side_proj = need(w.side_proj, "side.proj", {D, conf->side_dim});
+                L.side_norm = need(w.side_norm, "side.norm", {D});
+            }
+            // a ring holds the window's reach behind the first token of a pass, plus the pass
+            L.ring = c.window > 0 ? (int64_t)c.window - 1 + r->conf.chunk : std::max<int64_t>(r->conf.max_seq, r->conf.chunk);
+        }
+        // the order of the runs
+        const int n = conf->n_layers;
+        int a = conf->loop_start, b = conf->loop_stop, times = conf->loop_times;
+        if (times <= 1 || b <= a) { a = b = 0; times = 1; }
+        if (a < 0 || b > n) throw TensorError("the loop does not lie inside the layers");
+        for (int i = 0; i < a; i++) r->runs.push_back({i, false});
+        for (int t = 0; t < times; t++)
+            for (int i = a; i < b; i++) r->runs.push_back({i, t > 0 && i == a});
+        for (int i = b; i < n; i++) r->runs.push_back({i, false});
+        for (const Run& run : r->runs) {
+            const Layer& L = r->layers[run.layer];
+            r->state_bytes_per_slot += L.ring * ((int64_t)L.c.kv_rank + L.c.rot_dim) * 4;
+        }
+    });
+    if (rc != CC_OK) {
+        crabml::seq_set_create_error(err);
+        delete r;
+        return rc;
+    }
+    *out = r;
+    return CC_OK;
+}

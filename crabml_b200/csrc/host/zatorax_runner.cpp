@@ -16,7 +16,7 @@
 #include <vector>
 
 #include "../../../include/crabml_zatorax.h"
-#include "cuda_tensor.hpp"
+#include "seq_runner.hpp"
 
 using crabml::CudaTensor;
 using crabml::TensorError;
@@ -34,10 +34,8 @@ struct Layer {
 struct LayerState {
     CudaTensor kring, vring, S, tq, tk, tv;
 };
-struct Slot {
+struct State : crabml::SeqState {
     std::vector<LayerState> layers;
-    int64_t len = 0;
-    bool live = false;
 };
 
 cc_view view_of(const CudaTensor& t) { return t.view(); }
@@ -49,33 +47,24 @@ const cc_view* opt(const CudaTensor& t, cc_view& store) {
 
 }  // namespace
 
-struct czr_runner {
-    cc_device* dev = nullptr;
+// the sequence slots, the step function and greedy generation are the shared ones of seq_runner.hpp
+struct czr_runner_impl : csr_runner {
     czr_config conf{};
     std::vector<Layer> layers;
     CudaTensor embed, final_norm, head;
-    std::vector<Slot> slots;
-    int64_t state_bytes_per_slot = 0;
-    std::string last_error;
 
-    void check(int rc) { CudaTensor::check(dev, rc); }
-    CudaTensor adopt(cc_buf* b, std::vector<int64_t> shape) { return CudaTensor(dev, b, crabml::TensorStrider(std::move(shape))); }
-
-    void make_slot(Slot& s);
-    void reset_slot(Slot& s);
+    std::unique_ptr<crabml::SeqState> make_state() override;
+    void reset_state(crabml::SeqState& s) override;
+    CudaTensor forward_chunk(crabml::SeqState& s, int64_t pos0, const int64_t* tokens, int64_t n, int device_slot) override;
+    CudaTensor logits_of(const CudaTensor& x, const std::vector<int64_t>& rows) override;
     CudaTensor delta_mixer(const Layer& L, LayerState& st, const CudaTensor& x);
-    CudaTensor attention_mixer(int li, Slot& s, const CudaTensor& x, int64_t pos0);
+    CudaTensor attention_mixer(int li, State& s, const CudaTensor& x, int64_t pos0);
     CudaTensor feed_forward(const Layer& L, const CudaTensor& x);
-    CudaTensor forward_chunk(Slot& s, const int64_t* tokens, int64_t n, int device_slot);
-    CudaTensor logits_of(const CudaTensor& x, const std::vector<int64_t>& rows);
-    void step(int32_t slot, const int64_t* tokens, int32_t n, const int32_t* want, int32_t n_want, float* out);
-    Slot& slot_ref(int32_t slot) {
-        if (slot < 0 || slot >= (int32_t)slots.size() || !slots[slot].live) throw TensorError("sequence slot " + std::to_string(slot) + " is not open");
-        return slots[slot];
-    }
 };
 
-void czr_runner::make_slot(Slot& s) {
+std::unique_ptr<crabml::SeqState> czr_runner_impl::make_state() {
+    auto sp = std::make_unique<State>();
+    State& s = *sp;
     s.layers.resize(layers.size());
     for (size_t i = 0; i < layers.size(); i++) {
         const Layer& L = layers[i];
@@ -95,18 +84,18 @@ void czr_runner::make_slot(Slot& s) {
             }
         }
     }
+    return sp;
 }
 
 // a reused slot starts like a new one: the recurrence and the convolutions see zeros before position 0.  The rings need no reset:
 // a query at position i only reads rows of positions 0..i of ITS sequence, all written since the slot was opened.
-void czr_runner::reset_slot(Slot& s) {
-    for (auto& st : s.layers)
+void czr_runner_impl::reset_state(crabml::SeqState& base) {
+    for (auto& st : static_cast<State&>(base).layers)
         for (CudaTensor* t : {&st.S, &st.tq, &st.tk, &st.tv})
             if (t->valid()) { cc_view v = t->view(); check(cc_tensor_zero(dev, &v)); }
-    s.len = 0;
 }
 
-CudaTensor czr_runner::delta_mixer(const Layer& L, LayerState& st, const CudaTensor& x) {
+CudaTensor czr_runner_impl::delta_mixer(const Layer& L, LayerState& st, const CudaTensor& x) {
     const auto& c = L.c;
     const int64_t n = x.shape()[0];
     auto conv = [&](const CudaTensor& w, const CudaTensor& cw, CudaTensor& tail, int hs, bool unit, float scale) {
@@ -130,7 +119,7 @@ CudaTensor czr_runner::delta_mixer(const Layer& L, LayerState& st, const CudaTen
     return L.o.matmul_vec(o);
 }
 
-CudaTensor czr_runner::attention_mixer(int li, Slot& s, const CudaTensor& x, int64_t pos0) {
+CudaTensor czr_runner_impl::attention_mixer(int li, State& s, const CudaTensor& x, int64_t pos0) {
     const Layer& L = layers[li];
     const auto& c = L.c;
     const int64_t n = x.shape()[0];
@@ -150,7 +139,7 @@ CudaTensor czr_runner::attention_mixer(int li, Slot& s, const CudaTensor& x, int
     return L.o.matmul_vec(o);
 }
 
-CudaTensor czr_runner::feed_forward(const Layer& L, const CudaTensor& x) {
+CudaTensor czr_runner_impl::feed_forward(const Layer& L, const CudaTensor& x) {
     const auto& c = L.c;
     const int64_t n = x.shape()[0];
     cc_view xv = x.view(), rw = L.router.view(), cv{};
@@ -171,8 +160,8 @@ CudaTensor czr_runner::feed_forward(const Layer& L, const CudaTensor& x) {
 }
 
 // one pass over n <= chunk tokens at positions s.len .. ; returns the residual stream [n, width] after the last layer
-CudaTensor czr_runner::forward_chunk(Slot& s, const int64_t* tokens, int64_t n, int device_slot) {
-    const int64_t pos0 = s.len;
+CudaTensor czr_runner_impl::forward_chunk(crabml::SeqState& base, int64_t pos0, const int64_t* tokens, int64_t n, int device_slot) {
+    State& s = static_cast<State&>(base);
     CudaTensor x = CudaTensor::alloc({n, conf.width}, CC_F32, dev);
     if (device_slot >= 0) x.copy_rows_from_slot(embed, device_slot);
     else x.copy_rows_from(embed, std::vector<int64_t>(tokens, tokens + n));
@@ -190,11 +179,10 @@ CudaTensor czr_runner::forward_chunk(Slot& s, const int64_t* tokens, int64_t n, 
         }
         x = std::move(x).with_name("layer:" + std::to_string(li) + ":" + std::to_string(pos0));
     }
-    s.len += n;
     return x;
 }
 
-CudaTensor czr_runner::logits_of(const CudaTensor& x, const std::vector<int64_t>& rows) {
+CudaTensor czr_runner_impl::logits_of(const CudaTensor& x, const std::vector<int64_t>& rows) {
     const int64_t nw = (int64_t)rows.size();
     CudaTensor xs = CudaTensor::alloc({nw, conf.width}, CC_F32, dev);
     xs.copy_rows_from(x, rows);
@@ -204,50 +192,16 @@ CudaTensor czr_runner::logits_of(const CudaTensor& x, const std::vector<int64_t>
     return head.matmul_vec(xn);
 }
 
-void czr_runner::step(int32_t slot, const int64_t* tokens, int32_t n, const int32_t* want, int32_t n_want, float* out) {
-    Slot& s = slot_ref(slot);
-    for (int i = 0; i < n; i++)
-        if (tokens[i] < 0 || tokens[i] >= conf.vocab) throw TensorError("token id " + std::to_string(tokens[i]) + " is outside the vocabulary");
-    for (int i = 0; i < n_want; i++)
-        if (want[i] < 0 || want[i] >= n || (i > 0 && want[i] <= want[i - 1])) throw TensorError("wanted positions must be ascending indices into the step's tokens");
-    int wi = 0;
-    for (int64_t c0 = 0; c0 < n; c0 += conf.chunk) {
-        const int64_t cn = std::min<int64_t>(conf.chunk, n - c0);
-        CudaTensor x = forward_chunk(s, tokens + c0, cn, -1);
-        std::vector<int64_t> rows;
-        while (wi + (int)rows.size() < n_want && want[wi + rows.size()] < c0 + cn) rows.push_back(want[wi + rows.size()] - c0);
-        if (!rows.empty()) {
-            CudaTensor lg = logits_of(x, rows);
-            lg.export_to(out + (size_t)wi * conf.vocab, rows.size() * (size_t)conf.vocab);
-            wi += (int)rows.size();
-        }
-    }
-}
-
-static thread_local std::string g_create_error;
-
-template <class F>
-static int guarded(czr_runner* r, F&& f) {
-    try {
-        f();
-        return CC_OK;
-    } catch (const TensorError& e) {
-        if (r) r->last_error = e.what();
-        return CC_ERR_TENSOR;
-    } catch (const std::exception& e) {
-        if (r) r->last_error = e.what();
-        return CC_ERR_ARG;
-    }
-}
-
 extern "C" CC_API int czr_runner_create(cc_device* dev, const czr_config* conf, const czr_layer_config* lc, const czr_layer_weights* lw, cc_buf* embed, cc_buf* final_norm,
                                         cc_buf* head, czr_runner** out) {
     if (!dev || !conf || !lc || !lw || !embed || !final_norm || !head || !out) return CC_ERR_ARG;
-    czr_runner* r = new czr_runner();
+    czr_runner_impl* r = new czr_runner_impl();
     r->dev = dev;
     r->conf = *conf;
     if (r->conf.chunk <= 0) r->conf.chunk = 256;
-    int rc = guarded(r, [&] {
+    r->width = conf->width; r->vocab = conf->vocab; r->chunk = r->conf.chunk;
+    std::string err;
+    int rc = crabml::seq_guarded(r, &err, [&] {
         const int64_t D = conf->width;
         if (conf->n_layers < 1 || D < 1 || conf->vocab < 1) throw TensorError("bad model sizes");
         r->embed = CudaTensor::wrap(dev, embed, {conf->vocab, D});
@@ -317,7 +271,7 @@ extern "C" CC_API int czr_runner_create(cc_device* dev, const czr_config* conf, 
         }
     });
     if (rc != CC_OK) {
-        g_create_error = r->last_error;          // readable after the half-built runner is gone (czr_last_create_error)
+        crabml::seq_set_create_error(err);       // readable after the half-built runner is gone (csr_last_create_error)
         delete r;
         return rc;
     }
@@ -325,72 +279,18 @@ extern "C" CC_API int czr_runner_create(cc_device* dev, const czr_config* conf, 
     return CC_OK;
 }
 
-extern "C" CC_API const char* czr_last_create_error(void) { return g_create_error.c_str(); }
-extern "C" CC_API void czr_runner_destroy(czr_runner* r) { delete r; }
-extern "C" CC_API const char* czr_runner_last_error(czr_runner* r) { return r ? r->last_error.c_str() : ""; }
-
-extern "C" CC_API int czr_seq_open(czr_runner* r, int32_t* slot_out) {
-    if (!r || !slot_out) return CC_ERR_ARG;
-    return guarded(r, [&] {
-        int found = -1;
-        for (size_t i = 0; i < r->slots.size(); i++)
-            if (!r->slots[i].live) { found = (int)i; break; }            // lowest free slot first: closed slots are reused before new ones are made
-        if (found < 0) {
-            r->slots.emplace_back();
-            found = (int)r->slots.size() - 1;
-            r->make_slot(r->slots[found]);
-        }
-        r->reset_slot(r->slots[found]);
-        r->slots[found].live = true;
-        *slot_out = found;
-    });
-}
-extern "C" CC_API int czr_seq_close(czr_runner* r, int32_t slot) {
-    if (!r) return CC_ERR_ARG;
-    return guarded(r, [&] { r->slot_ref(slot).live = false; });
-}
-extern "C" CC_API int64_t czr_seq_len(czr_runner* r, int32_t slot) {
-    if (!r || slot < 0 || slot >= (int32_t)r->slots.size() || !r->slots[slot].live) return -1;
-    return r->slots[slot].len;
-}
-extern "C" CC_API int czr_runner_stats(czr_runner* r, int64_t* out3) {
-    if (!r || !out3) return CC_ERR_ARG;
-    out3[0] = (int64_t)r->slots.size();
-    out3[1] = 0;
-    for (auto& s : r->slots) out3[1] += s.live;
-    out3[2] = r->state_bytes_per_slot;
-    return CC_OK;
-}
-
+// the family's older names of the shared entry points
+extern "C" CC_API const char* czr_last_create_error(void) { return csr_last_create_error(); }
+extern "C" CC_API void czr_runner_destroy(czr_runner* r) { csr_runner_destroy(r); }
+extern "C" CC_API const char* czr_runner_last_error(czr_runner* r) { return csr_runner_last_error(r); }
+extern "C" CC_API int czr_seq_open(czr_runner* r, int32_t* slot_out) { return csr_seq_open(r, slot_out); }
+extern "C" CC_API int czr_seq_close(czr_runner* r, int32_t slot) { return csr_seq_close(r, slot); }
+extern "C" CC_API int64_t czr_seq_len(czr_runner* r, int32_t slot) { return csr_seq_len(r, slot); }
+extern "C" CC_API int czr_runner_stats(czr_runner* r, int64_t* out3) { return csr_runner_stats(r, out3); }
 extern "C" CC_API int czr_runner_step(czr_runner* r, int32_t slot, const int64_t* tokens, int32_t n_tokens, const int32_t* want, int32_t n_want, float* logits_out) {
-    if (!r || !tokens || n_tokens < 1 || n_want < 0 || (n_want > 0 && (!want || !logits_out))) return CC_ERR_ARG;
-    return guarded(r, [&] { r->step(slot, tokens, n_tokens, want, n_want, logits_out); });
+    return csr_runner_step(r, slot, tokens, n_tokens, want, n_want, logits_out);
 }
-
 extern "C" CC_API int czr_runner_generate_greedy(czr_runner* r, int32_t slot, const int64_t* prompt, int32_t n_prompt, int32_t steps, int64_t eos, int64_t* out_tokens,
                                                  int32_t* n_out) {
-    if (!r || !prompt || n_prompt < 1 || steps < 1 || !out_tokens || !n_out) return CC_ERR_ARG;
-    *n_out = 0;
-    return guarded(r, [&] {
-        Slot& s = r->slot_ref(slot);
-        for (int i = 0; i < n_prompt; i++)
-            if (prompt[i] < 0 || prompt[i] >= r->conf.vocab) throw TensorError("token id outside the vocabulary");
-        CudaTensor x;
-        int64_t last_n = 0;
-        for (int64_t c0 = 0; c0 < n_prompt; c0 += r->conf.chunk) {
-            last_n = std::min<int64_t>(r->conf.chunk, n_prompt - c0);
-            x = r->forward_chunk(s, prompt + c0, last_n, -1);
-        }
-        r->logits_of(x, {last_n - 1}).reshape({r->conf.vocab}).argmax_to_slot(0, 0);
-        int64_t done = 1;
-        if (eos >= 0) r->check(cc_read_history(r->dev, 0, 1, out_tokens));
-        for (; done < steps; done++) {
-            if (eos >= 0 && out_tokens[done - 1] == eos) break;
-            x = r->forward_chunk(s, nullptr, 1, 0);
-            r->logits_of(x, {0}).reshape({r->conf.vocab}).argmax_to_slot(0, done);
-            if (eos >= 0) r->check(cc_read_history(r->dev, done, 1, out_tokens + done));
-        }
-        if (eos < 0) r->check(cc_read_history(r->dev, 0, done, out_tokens));
-        *n_out = (int32_t)done;
-    });
+    return csr_runner_generate_greedy(r, slot, prompt, n_prompt, steps, eos, out_tokens, n_out);
 }

@@ -37,7 +37,7 @@ __device__ __forceinline__ void warp_argmax(float& v, int& idx) {
 // one CTA per token: its warps share the experts' logits (a warp per expert, lanes striding D), then warp 0 does the softmax and the choice
 __global__ void __launch_bounds__(RT_WARPS * 32) moe_route_kernel(const float* __restrict__ x, const float* __restrict__ wr, const float* __restrict__ corr,
                                                                   int* __restrict__ ids, float* __restrict__ wts, int T, int D, int E, int top, int n_groups, int keep,
-                                                                  int renorm) {
+                                                                  int renorm, int score_fn, int group_top, float renorm_eps) {
     extern __shared__ float rt_sm[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
@@ -54,21 +54,35 @@ __global__ void __launch_bounds__(RT_WARPS * 32) moe_route_kernel(const float* _
     }
     __syncthreads();
     if (warp != 0) return;
-    float mx = -INFINITY;
-    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
-    mx = warp_max(mx);
-    __syncwarp();
-    float sum = 0.0f;
-    for (int e = lane; e < E; e += 32) { const float v = expf(s[e] - mx); s[e] = v; sum += v; }
-    sum = warp_sum(sum);
-    const float inv = 1.0f / sum;
-    for (int e = lane; e < E; e += 32) { const float v = s[e] * inv; s[e] = v; c[e] = corr ? v + corr[e] : v; }
+    if (score_fn == CC_ROUTE_SIGMOID) {
+        for (int e = lane; e < E; e += 32) { const float v = 1.0f / (1.0f + expf(-s[e])); s[e] = v; c[e] = corr ? v + corr[e] : v; }
+    } else {
+        float mx = -INFINITY;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
+        mx = warp_max(mx);
+        __syncwarp();
+        float sum = 0.0f;
+        for (int e = lane; e < E; e += 32) { const float v = expf(s[e] - mx); s[e] = v; sum += v; }
+        sum = warp_sum(sum);
+        const float inv = 1.0f / sum;
+        for (int e = lane; e < E; e += 32) { const float v = s[e] * inv; s[e] = v; c[e] = corr ? v + corr[e] : v; }
+    }
     __syncwarp();
     if (n_groups > 1) {
         const int per = E / n_groups;
         for (int g = lane; g < n_groups; g += 32) {
-            float m = -INFINITY;
-            for (int e = 0; e < per; e++) m = fmaxf(m, c[g * per + e]);
+            // the group's score: the sum of its group_top largest choice scores, largest first (picked in order: below the last
+            // pick, or equal to it at a higher index)
+            float m = 0.0f, lv = INFINITY; int li = -1;
+            for (int n = 0; n < group_top; n++) {
+                float bv = -INFINITY; int bi = -1;
+                for (int e = 0; e < per; e++) {
+                    const float v = c[g * per + e];
+                    if ((v < lv || (v == lv && e > li)) && (bi < 0 || v > bv)) { bv = v; bi = e; }
+                }
+                if (bi < 0) break;
+                m = n == 0 ? bv : m + bv; lv = bv; li = bi;
+            }
             gs[g] = m;
         }
         __syncwarp();
@@ -97,11 +111,15 @@ __global__ void __launch_bounds__(RT_WARPS * 32) moe_route_kernel(const float* _
         wsum += s[bi];
         __syncwarp();
     }
-    if (renorm && lane == 0) for (int r = 0; r < top; r++) wts[(int64_t)t * top + r] /= wsum;
+    if (renorm && lane == 0) for (int r = 0; r < top; r++) wts[(int64_t)t * top + r] /= wsum + renorm_eps;
 }
-extern "C" CC_API int cc_moe_route(cc_device* dev, const cc_view* x, const cc_view* router_w, const cc_view* correction, int32_t top, int32_t n_groups,
-                                   int32_t keep_groups, int32_t renormalise, cc_buf** ids_out, cc_buf** weights_out) {
+extern "C" CC_API int cc_moe_route_ex(cc_device* dev, const cc_view* x, const cc_view* router_w, const cc_view* correction, const cc_route_params* rp, cc_buf** ids_out,
+                                      cc_buf** weights_out) {
     MOE_ENTER(dev, "moe_route");
+    if (!rp) return cc_fail(dev, CC_ERR_ARG, "moe_route: no parameters");
+    int32_t top = rp->top, n_groups = rp->n_groups, keep_groups = rp->keep_groups;
+    const int32_t renormalise = rp->renormalise, group_top = rp->group_top < 1 ? 1 : rp->group_top;
+    CC_REQUIRE(dev, rp->score == CC_ROUTE_SOFTMAX || rp->score == CC_ROUTE_SIGMOID, "moe_route: unknown score function %d", rp->score);
     if (!ids_out || !weights_out) return cc_fail(dev, CC_ERR_ARG, "moe_route: out is NULL");
     MOE_VIEW(dev, x, "moe_route x"); MOE_VIEW(dev, router_w, "moe_route router_w");
     REQUIRE_F32(dev, x, "moe_route x"); REQUIRE_F32(dev, router_w, "moe_route router_w");
@@ -124,9 +142,14 @@ extern "C" CC_API int cc_moe_route(cc_device* dev, const cc_view* x, const cc_vi
     moe_route_kernel<<<(unsigned)T, RT_WARPS * 32, smem, dev->stream>>>((const float*)x->buf->plane[0], (const float*)router_w->buf->plane[0],
                                                                                                      correction ? (const float*)correction->buf->plane[0] : nullptr,
                                                                                                      (int*)ids->base, (float*)wts->base, (int)T, (int)D, (int)E, top, n_groups,
-                                                                                                     keep_groups, renormalise);
+                                                                                                     keep_groups, renormalise, rp->score, group_top, rp->renorm_eps);
     CC_LAUNCH_CHECK(dev);
     return CC_OK;
+}
+extern "C" CC_API int cc_moe_route(cc_device* dev, const cc_view* x, const cc_view* router_w, const cc_view* correction, int32_t top, int32_t n_groups,
+                                   int32_t keep_groups, int32_t renormalise, cc_buf** ids_out, cc_buf** weights_out) {
+    const cc_route_params rp = {CC_ROUTE_SOFTMAX, top, n_groups, keep_groups, 1, renormalise, 0.0f};
+    return cc_moe_route_ex(dev, x, router_w, correction, &rp, ids_out, weights_out);
 }
 
 // ---- experts ---------------------------------------------------------------------------------------------------------------------------
@@ -138,14 +161,20 @@ template <class WT> __device__ __forceinline__ float moe_round(float v);
 template <> __device__ __forceinline__ float moe_round<float>(float v) { return v; }
 template <> __device__ __forceinline__ float moe_round<uint16_t>(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
-__device__ __forceinline__ float moe_act(float z, int act) {
-    return act == CC_ACT_SILU ? z / (1.0f + expf(-z)) : act == CC_ACT_GELU_TANH ? 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))) : z;
+__device__ __forceinline__ float moe_act(float z, int act, float alpha) {
+    return act == CC_ACT_SILU ? z / (1.0f + expf(-z)) : act == CC_ACT_GELU_TANH ? 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)))
+         : act == CC_ACT_SWISH ? z / (1.0f + expf(-(alpha * z))) : z;
+}
+// the gated unit: act(min(g, limit)) * (clamp(u, -limit, limit) + up_shift); limit <= 0 clamps nothing
+__device__ __forceinline__ float moe_glu(float g, float u, const cc_glu_params P) {
+    if (P.limit > 0.0f) { g = fminf(g, P.limit); u = fminf(fmaxf(u, -P.limit), P.limit); }
+    return moe_act(g, P.act, P.alpha) * (u + P.up_shift);
 }
 
 // grid (T * top, ceil(ff / 8)), 256 threads: the CTA stages x[t] (rounded for BF16 weights); a warp owns one hidden row of the slot's expert
 template <class WT>
 __global__ void __launch_bounds__(256) moe_gate_up_kernel(const float* __restrict__ x, const int* __restrict__ ids, const WT* __restrict__ wg, const WT* __restrict__ wu,
-                                                          float* __restrict__ hid, int D, int ff, int top, int act, int E) {
+                                                          float* __restrict__ hid, int D, int ff, int top, cc_glu_params act, int E) {
     extern __shared__ float mg_sm[];
     const int ts = blockIdx.x, t = ts / top;
     const int e = moe_clamp(ids[ts], E);
@@ -157,7 +186,7 @@ __global__ void __launch_bounds__(256) moe_gate_up_kernel(const float* __restric
     float g = 0.0f, u = 0.0f;
     for (int d = lane; d < D; d += 32) { const float xv = mg_sm[d]; g = fmaf(moe_w(wg, base + d), xv, g); u = fmaf(moe_w(wu, base + d), xv, u); }
     g = warp_sum(g); u = warp_sum(u);
-    if (lane == 0) hid[(int64_t)ts * ff + r] = moe_act(g, act) * u;
+    if (lane == 0) hid[(int64_t)ts * ff + r] = moe_glu(g, u, act);
 }
 // grid (T, ceil(D / 8)), 256 threads: the CTA stages the token's top hidden rows; a warp owns one output coordinate and adds the slots in order
 template <class WT>
@@ -183,7 +212,7 @@ __global__ void __launch_bounds__(256) moe_down_kernel(const float* __restrict__
 
 template <class WT>
 static int moe_launch(cc_device* dev, const float* x, const int* ids, const float* wts, const void* wg, const void* wu, const void* wd, float* hid, float* out, int64_t T,
-                      int D, int ff, int top, int act, int E) {
+                      int D, int ff, int top, cc_glu_params act, int E) {
     const size_t s1 = (size_t)D * 4, s2 = (size_t)top * ff * 4;
     if (s1 > 200 * 1024 || s2 > 200 * 1024) return cc_fail(dev, CC_ERR_UNSUPPORTED, "moe_experts: row does not fit shared memory");
     if (s1 > 48 * 1024) CC_CUDA(dev, cudaFuncSetAttribute(moe_gate_up_kernel<WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s1));
@@ -235,10 +264,10 @@ __global__ void moe_gather_bf16_kernel(const float* __restrict__ x, const int* _
     __nv_bfloat16* dst = xs + (int64_t)pos[i] * D;
     for (int d = lane * 2; d < D; d += 64) *(__nv_bfloat162*)(dst + d) = __floats2bfloat162_rn(src[d], src[d + 1]);
 }
-__global__ void moe_glu_bf16_kernel(const float* __restrict__ g, const float* __restrict__ u, __nv_bfloat16* __restrict__ h, int64_t n, int act) {
+__global__ void moe_glu_bf16_kernel(const float* __restrict__ g, const float* __restrict__ u, __nv_bfloat16* __restrict__ h, int64_t n, cc_glu_params act) {
     const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 2;
     if (i >= n) return;
-    *(__nv_bfloat162*)(h + i) = __floats2bfloat162_rn(moe_act(g[i], act) * u[i], moe_act(g[i + 1], act) * u[i + 1]);
+    *(__nv_bfloat162*)(h + i) = __floats2bfloat162_rn(moe_glu(g[i], u[i], act), moe_glu(g[i + 1], u[i + 1], act));
 }
 // out[t][d] = sum over the slots, in slot order, of weights[t][s] * y[pos[t * top + s]][d]
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos, const float* __restrict__ wts, float* __restrict__ out, int64_t T, int top, int D) {
@@ -251,7 +280,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
 }
 
 static int moe_grouped(cc_device* dev, const float* x, const int* ids, const float* wts, const cc_buf* wg, const cc_buf* wu, const cc_buf* wd, float* out, int64_t T, int D,
-                       int ff, int top, int E, int act) {
+                       int ff, int top, int E, cc_glu_params act) {
     const int64_t n = T * top;
     const int block_n = n / E >= 96 ? 128 : 64;
     const int max_tiles = (int)((n + block_n - 1) / block_n) + E;
@@ -284,9 +313,11 @@ static int moe_grouped(cc_device* dev, const float* x, const int* ids, const flo
     return rc;
 }
 
-extern "C" CC_API int cc_moe_experts(cc_device* dev, const cc_view* x, const cc_view* ids, const cc_view* weights, const cc_view* w_gate, const cc_view* w_up,
-                                     const cc_view* w_down, int32_t n_experts, int32_t ff, int32_t act, cc_buf** out) {
+extern "C" CC_API int cc_moe_experts_glu(cc_device* dev, const cc_view* x, const cc_view* ids, const cc_view* weights, const cc_view* w_gate, const cc_view* w_up,
+                                         const cc_view* w_down, int32_t n_experts, int32_t ff, const cc_glu_params* glu, cc_buf** out) {
     MOE_ENTER(dev, "moe_experts");
+    if (!glu) return cc_fail(dev, CC_ERR_ARG, "moe_experts: no gated-unit parameters");
+    const cc_glu_params act = *glu;
     if (!out) return cc_fail(dev, CC_ERR_ARG, "moe_experts: out is NULL");
     MOE_VIEW(dev, x, "moe_experts x"); MOE_VIEW(dev, ids, "moe_experts ids"); MOE_VIEW(dev, weights, "moe_experts weights");
     MOE_VIEW(dev, w_gate, "moe_experts w_gate"); MOE_VIEW(dev, w_up, "moe_experts w_up"); MOE_VIEW(dev, w_down, "moe_experts w_down");
@@ -319,4 +350,9 @@ extern "C" CC_API int cc_moe_experts(cc_device* dev, const cc_view* x, const cc_
     else rc = moe_launch<uint16_t>(dev, xp, ip, wp, w_gate->buf->plane[0], w_up->buf->plane[0], w_down->buf->plane[0], (float*)hid, (float*)o->base, T, (int)D, ff, (int)top, act, n_experts);
     cc_pool_free(dev, hid, cls);
     return rc;
+}
+extern "C" CC_API int cc_moe_experts(cc_device* dev, const cc_view* x, const cc_view* ids, const cc_view* weights, const cc_view* w_gate, const cc_view* w_up,
+                                     const cc_view* w_down, int32_t n_experts, int32_t ff, int32_t act, cc_buf** out) {
+    const cc_glu_params glu = {act, 1.0f, 0.0f, 0.0f};
+    return cc_moe_experts_glu(dev, x, ids, weights, w_gate, w_up, w_down, n_experts, ff, &glu, out);
 }

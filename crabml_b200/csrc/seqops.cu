@@ -431,6 +431,7 @@ extern "C" CC_API int cc_kv_ring_append(cc_device* dev, const cc_view* kring, co
 #define WA_THREADS 256
 struct WaGeom {
     int T, H, G, R, dk, dv, window, ring, QT, cap;      // QT queries per tile; cap = row stride of S
+    int krs, vrs, vhs;                                  // floats between two rows of the key / value ring (vhs: between two heads' values inside a row)
     int64_t pos0;
 };
 __device__ __forceinline__ int64_t wa_lo(const WaGeom& g, int64_t i) { return (g.window > 0 && i - g.window + 1 > 0) ? i - g.window + 1 : 0; }
@@ -473,7 +474,7 @@ __global__ void __launch_bounds__(WA_THREADS) wa_scores_kernel(const float* __re
             const bool din = d0 + dd < g.dk;
             sq[dd][r] = (din && tq < tq_n) ? q[((int64_t)(t0 + tq) * g.H + kvh * g.R + hr) * g.dk + d0 + dd] : 0.0f;
             const int64_t j = j0 + r;
-            sk[dd][r] = (din && j <= i_last) ? kring[((j % g.ring) * g.G + kvh) * g.dk + d0 + dd] : 0.0f;
+            sk[dd][r] = (din && j <= i_last) ? kring[(j % g.ring) * g.krs + kvh * g.dk + d0 + dd] : 0.0f;
         }
         __syncthreads();
 #pragma unroll
@@ -507,7 +508,8 @@ __global__ void __launch_bounds__(WA_THREADS) wa_scores_kernel(const float* __re
     }
 }
 // one warp per row
-__global__ void wa_softmax_kernel(float* __restrict__ S, WaGeom g) {
+// sink != NULL: the denominator also holds exp(sink[head]), a key without a value whose score is sink[head] as it stands (no scale)
+__global__ void wa_softmax_kernel(float* __restrict__ S, WaGeom g, const float* __restrict__ sink) {
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (row >= (int64_t)g.T * g.H) return;
@@ -517,9 +519,12 @@ __global__ void wa_softmax_kernel(float* __restrict__ S, WaGeom g) {
     float mx = -INFINITY;
     for (int c = lane; c < n; c += 32) mx = fmaxf(mx, Sr[c]);
     mx = warp_max(mx);
+    const float sk = sink ? sink[row % g.H] : -INFINITY;
+    mx = fmaxf(mx, sk);
     float sum = 0.0f;
     for (int c = lane; c < n; c += 32) { const float e = expf(Sr[c] - mx); Sr[c] = e; sum += e; }
     sum = warp_sum(sum);
+    if (sink) sum += expf(sk - mx);
     const float inv = 1.0f / sum;
     for (int c = lane; c < n; c += 32) Sr[c] *= inv;
 }
@@ -540,10 +545,10 @@ __global__ void __launch_bounds__(128) wa_values_row_kernel(const float* __restr
     const int per = (n + 3) >> 2;
     const int c_begin = min(n, w * per), c_end = min(n, c_begin + per);
     const int r0 = (int)(lo % g.ring);
-    const int64_t rs = (int64_t)g.G * g.dv;
+    const int64_t rs = g.vrs;
     float acc = 0.0f;
     if (d < g.dv) {
-        const float* vb = vring + (int64_t)kvh * g.dv + d;
+        const float* vb = vring + (int64_t)kvh * g.vhs + d;
         int r = r0 + c_begin;
         if (r >= g.ring) r -= g.ring;
 #pragma unroll 8
@@ -587,7 +592,7 @@ __global__ void __launch_bounds__(WA_THREADS) wa_values_kernel(const float* __re
             {   // values: consecutive threads read consecutive columns of one key
                 const int kk = idx >> 6, c = idx & 63;
                 const int64_t j = j0 + kk;
-                sv[kk][c] = (j <= i_last && c0 + c < g.dv) ? vring[((j % g.ring) * g.G + kvh) * g.dv + c0 + c] : 0.0f;
+                sv[kk][c] = (j <= i_last && c0 + c < g.dv) ? vring[(j % g.ring) * g.vrs + kvh * g.vhs + c0 + c] : 0.0f;
             }
         }
         __syncthreads();
@@ -615,12 +620,14 @@ __global__ void __launch_bounds__(WA_THREADS) wa_values_kernel(const float* __re
         }
     }
 }
-extern "C" CC_API int cc_window_attention(cc_device* dev, const cc_view* q, const cc_view* qnw, float eps, const cc_view* kring, const cc_view* vring, int64_t pos0,
-                                          int32_t H, int32_t G, int32_t dk, int32_t dv, int32_t window, float scale, const cc_view* r1, const cc_view* r2,
-                                          cc_buf** out) {
+extern "C" CC_API int cc_window_attention_sink(cc_device* dev, const cc_view* q, const cc_view* qnw, float eps, const cc_view* kring, const cc_view* vring, int64_t pos0,
+                                               int32_t H, int32_t G, int32_t dk, int32_t dv, int32_t window, float scale, const cc_view* r1, const cc_view* r2,
+                                               const cc_view* sink, cc_buf** out) {
     SEQ_ENTER(dev, "window_attention");
     if (!out) return cc_fail(dev, CC_ERR_ARG, "window_attention: out is NULL");
-    SEQ_F32(dev, q, "window_attention q"); SEQ_F32(dev, kring, "window_attention kring"); SEQ_F32(dev, vring, "window_attention vring");
+    SEQ_F32(dev, q, "window_attention q"); SEQ_F32(dev, kring, "window_attention kring");
+    if (vring) SEQ_F32(dev, vring, "window_attention vring");
+    if (sink) { SEQ_F32(dev, sink, "window_attention sink"); CC_REQUIRE(dev, view_len(sink) == H, "window_attention: sink must have one number per head"); }
     if (qnw) { SEQ_F32(dev, qnw, "window_attention q_norm_w"); CC_REQUIRE(dev, view_len(qnw) == dk, "window_attention: q_norm_w must have dk elements"); }
     CC_REQUIRE(dev, (r1 == nullptr) == (r2 == nullptr), "window_attention: r1 and r2 come together");
     if (r1) {
@@ -629,8 +636,9 @@ extern "C" CC_API int cc_window_attention(cc_device* dev, const cc_view* q, cons
     }
     CC_REQUIRE(dev, H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0 && q->ndim == 2 && kring->ndim == 2 && pos0 >= 0, "window_attention: bad arguments");
     const int64_t T = q->shape[0], ring = kring->shape[0];
-    CC_REQUIRE(dev, view_len(q) == T * H * dk && view_len(kring) == ring * G * dk && view_len(vring) == ring * G * dv,
+    CC_REQUIRE(dev, view_len(q) == T * H * dk && view_len(kring) == ring * G * dk && (vring ? view_len(vring) == ring * G * dv : dv <= dk),
                "window_attention: operand sizes do not fit heads=%d kv=%d dk=%d dv=%d", H, G, dk, dv);
+    const float* vptr = vring ? fptr(vring) : fptr(kring);            // no value ring: a key row's first dv columns are its value
     // the oldest row the first query needs must not have been overwritten by the newest row of this call
     const int64_t last = pos0 + T - 1;
     const int64_t oldest = window > 0 ? (pos0 - window + 1 > 0 ? pos0 - window + 1 : 0) : 0;
@@ -646,6 +654,7 @@ extern "C" CC_API int cc_window_attention(cc_device* dev, const cc_view* q, cons
     CC_REQUIRE(dev, R <= WA_TILE, "window_attention: %d query heads per key/value head (at most %d)", R, WA_TILE);
     WaGeom g;
     g.T = (int)T; g.H = H; g.G = G; g.R = R; g.dk = dk; g.dv = dv; g.window = window; g.ring = (int)ring; g.QT = WA_TILE / R; g.cap = (int)maxn; g.pos0 = pos0;
+    g.krs = G * dk; g.vrs = vring ? G * dv : G * dk; g.vhs = vring ? dv : dk;
     float* qp = fptr(q);
     if (qnw) {             // the query norm, in place: q is this call's private projection output in every caller of the runner; a caller that
                            // needs its q untouched passes a copy
@@ -661,17 +670,290 @@ extern "C" CC_API int cc_window_attention(cc_device* dev, const cc_view* q, cons
     dim3 g1((unsigned)((band_max + WA_TILE - 1) / WA_TILE), (unsigned)q_tiles, (unsigned)G);
     wa_scores_kernel<<<g1, WA_THREADS, 0, dev->stream>>>(qp, fptr(kring), (float*)Sp, g, scale, r1 ? fptr(r1) : nullptr, r2 ? fptr(r2) : nullptr);
     dev->launches++;
-    wa_softmax_kernel<<<(unsigned)((T * H + 7) / 8), 256, 0, dev->stream>>>((float*)Sp, g);
+    wa_softmax_kernel<<<(unsigned)((T * H + 7) / 8), 256, 0, dev->stream>>>((float*)Sp, g, sink ? fptr(sink) : nullptr);
     dev->launches++;
     if (T * H <= 64 && (size_t)maxn * 4 <= 160 * 1024) {
         const size_t smem = (size_t)maxn * 4;
         if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(wa_values_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) { cc_pool_free(dev, Sp, cls); return cc_fail(dev, CC_ERR_CUDA, "window_attention: %s", cudaGetErrorString(e)); } }
-        wa_values_row_kernel<<<dim3((unsigned)(T * H), (unsigned)((dv + 31) / 32)), 128, smem, dev->stream>>>((const float*)Sp, fptr(vring), (float*)o->base, g);
+        wa_values_row_kernel<<<dim3((unsigned)(T * H), (unsigned)((dv + 31) / 32)), 128, smem, dev->stream>>>((const float*)Sp, vptr, (float*)o->base, g);
     } else {
         dim3 g3((unsigned)((dv + WA_TILE - 1) / WA_TILE), (unsigned)q_tiles, (unsigned)G);
-        wa_values_kernel<<<g3, WA_THREADS, 0, dev->stream>>>((const float*)Sp, fptr(vring), (float*)o->base, g);
+        wa_values_kernel<<<g3, WA_THREADS, 0, dev->stream>>>((const float*)Sp, vptr, (float*)o->base, g);
     }
     cc_pool_free(dev, Sp, cls);
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}
+extern "C" CC_API int cc_window_attention(cc_device* dev, const cc_view* q, const cc_view* qnw, float eps, const cc_view* kring, const cc_view* vring, int64_t pos0,
+                                          int32_t H, int32_t G, int32_t dk, int32_t dv, int32_t window, float scale, const cc_view* r1, const cc_view* r2,
+                                          cc_buf** out) {
+    if (dev && !vring) return cc_fail(dev, CC_ERR_ARG, "window_attention: vring is NULL");
+    return cc_window_attention_sink(dev, q, qnw, eps, kring, vring, pos0, H, G, dk, dv, window, scale, r1, r2, nullptr, out);
+}
+
+// ---- RMS norm in groups ----------------------------------------------------------------------------------------------------------------
+// one warp per (row, group): the units are consecutive in memory, unit u covers x[u * gs, (u + 1) * gs)
+__global__ void group_rms_norm_kernel(float* __restrict__ dst, const float* __restrict__ x, const float* __restrict__ w, int64_t n_units, int groups, int gs, float eps) {
+    const int64_t u = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (u >= n_units) return;
+    const float* xr = x + u * gs;
+    const float* wr = w + (u % groups) * gs;
+    float ss = 0.0f;
+    for (int c = lane; c < gs; c += 32) ss = fmaf(xr[c], xr[c], ss);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)gs + eps);
+    float* dr = dst + u * gs;
+    for (int c = lane; c < gs; c += 32) dr[c] = xr[c] * inv * wr[c];
+}
+extern "C" CC_API int cc_group_rms_norm(cc_device* dev, const cc_view* dst, const cc_view* x, const cc_view* w, int32_t groups, float eps) {
+    SEQ_ENTER(dev, "group_rms_norm");
+    SEQ_F32(dev, dst, "group_rms_norm dst"); SEQ_F32(dev, x, "group_rms_norm x"); SEQ_F32(dev, w, "group_rms_norm w");
+    CC_REQUIRE(dev, x->ndim == 2 && dst->ndim == 2 && dst->shape[0] == x->shape[0] && dst->shape[1] == x->shape[1], "group_rms_norm: dst and x must be [rows, cols]");
+    const int64_t rows = x->shape[0], cols = x->shape[1];
+    CC_REQUIRE(dev, groups >= 1 && cols % groups == 0 && view_len(w) == cols, "group_rms_norm: %lld columns, %d groups, %lld weights", (long long)cols, groups, (long long)view_len(w));
+    if (rows == 0) return CC_OK;
+    const int64_t units = rows * groups;
+    group_rms_norm_kernel<<<(unsigned)((units + 7) / 8), 256, 0, dev->stream>>>(fptr(dst), fptr(x), fptr(w), units, groups, (int)(cols / groups), eps);
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}
+
+// ---- rotary positions from a frequency table, neighbouring coordinates paired -------------------------------------------------------------
+// the angle is the 32-bit product of the position and the pair's frequency; cosf / sinf are the accurate library functions
+__device__ __forceinline__ void rotate_pair(float u, float v, float pos, float f, float mag, float& ou, float& ov) {
+    const float a = pos * f;
+    const float c = cosf(a) * mag, s = sinf(a) * mag;
+    ou = u * c - v * s;
+    ov = v * c + u * s;
+}
+// one thread per (token, head, pair)
+__global__ void rope_pairs_kernel(float* __restrict__ x, const float* __restrict__ freq, int64_t n, int heads, int hs, int off, int half, float mag, int64_t pos0) {
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    const int i = (int)(idx % half);
+    const int64_t th = idx / half;                                   // token * heads + head
+    float* p = x + th * hs + off + 2 * i;
+    float ou, ov;
+    rotate_pair(p[0], p[1], (float)(pos0 + th / heads), freq[i], mag, ou, ov);
+    p[0] = ou; p[1] = ov;
+}
+extern "C" CC_API int cc_rope_pairs(cc_device* dev, const cc_view* x, int32_t n_heads, int32_t head_size, int32_t offset, const cc_view* freq, float mag, int64_t pos0) {
+    SEQ_ENTER(dev, "rope_pairs");
+    SEQ_F32(dev, x, "rope_pairs x"); SEQ_F32(dev, freq, "rope_pairs freq");
+    const int64_t half = view_len(freq);
+    CC_REQUIRE(dev, x->ndim == 2 && n_heads > 0 && head_size > 0 && x->shape[1] == (int64_t)n_heads * head_size && offset >= 0 && offset + 2 * half <= head_size && pos0 >= 0,
+               "rope_pairs: %lld pairs at column %d do not fit heads of %d", (long long)half, offset, head_size);
+    const int64_t n = x->shape[0] * n_heads * half;
+    if (n == 0) return CC_OK;
+    rope_pairs_kernel<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>(fptr(x), fptr(freq), n, n_heads, head_size, offset, (int)half, mag, pos0);
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}
+
+// ---- latent key/value cache ------------------------------------------------------------------------------------------------------------------
+// one warp per token: the first `rank` columns are RMS-normalised and weighted, the pairs of the next columns rotated, the rest copied
+__global__ void latent_ring_append_kernel(float* __restrict__ ring, const float* __restrict__ ckv, const float* __restrict__ nw, const float* __restrict__ freq, float eps,
+                                          float mag, int64_t pos0, int ring_rows, int T, int rank, int rest, int half) {
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= T) return;
+    const int cols = rank + rest;
+    const float* src = ckv + (int64_t)t * cols;
+    float* dst = ring + ((pos0 + t) % ring_rows) * cols;
+    float ss = 0.0f;
+    for (int c = lane; c < rank; c += 32) ss = fmaf(src[c], src[c], ss);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)rank + eps);
+    for (int c = lane; c < rank; c += 32) dst[c] = src[c] * inv * (nw ? nw[c] : 1.0f);
+    for (int i = lane; i < half; i += 32) {
+        float ou, ov;
+        rotate_pair(src[rank + 2 * i], src[rank + 2 * i + 1], (float)(pos0 + t), freq[i], mag, ou, ov);
+        dst[rank + 2 * i] = ou; dst[rank + 2 * i + 1] = ov;
+    }
+    for (int c = rank + 2 * half + lane; c < cols; c += 32) dst[c] = src[c];
+}
+extern "C" CC_API int cc_latent_ring_append(cc_device* dev, const cc_view* ring, const cc_view* ckv, const cc_view* norm_w, float eps, int32_t rank, const cc_view* freq,
+                                            float mag, int64_t pos0) {
+    SEQ_ENTER(dev, "latent_ring_append");
+    SEQ_F32(dev, ring, "latent_ring_append ring"); SEQ_F32(dev, ckv, "latent_ring_append ckv");
+    if (norm_w) SEQ_F32(dev, norm_w, "latent_ring_append norm_w");
+    if (freq) SEQ_F32(dev, freq, "latent_ring_append freq");
+    CC_REQUIRE(dev, ring->ndim == 2 && ckv->ndim == 2 && ring->shape[1] == ckv->shape[1] && pos0 >= 0, "latent_ring_append: ring and rows must be 2-D with equal columns");
+    const int64_t cols = ckv->shape[1], T = ckv->shape[0], half = freq ? view_len(freq) : 0;
+    CC_REQUIRE(dev, rank >= 1 && rank + 2 * half <= cols && (!norm_w || view_len(norm_w) == rank), "latent_ring_append: rank %d + %lld rotated pairs do not fit %lld columns", rank,
+               (long long)half, (long long)cols);
+    CC_REQUIRE(dev, T <= ring->shape[0], "latent_ring_append: %lld tokens do not fit a ring of %lld", (long long)T, (long long)ring->shape[0]);
+    if (T == 0) return CC_OK;
+    latent_ring_append_kernel<<<(unsigned)((T + 7) / 8), 256, 0, dev->stream>>>(fptr(ring), fptr(ckv), norm_w ? fptr(norm_w) : nullptr, freq ? fptr(freq) : nullptr, eps, mag, pos0,
+                                                                                  (int)ring->shape[0], (int)T, rank, (int)(cols - rank), (int)half);
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}
+
+// ---- per-head products that fold a latent cache's up-projections into the query and the output -----------------------------------------------------
+#define HP_TOK 8
+// grid (ceil(T / 8), H): the CTA stages 8 tokens' q[t, h, :dim]; thread r owns latent coordinate r for those tokens and walks d upwards, so a
+// result's sum order does not depend on T or on the token's place in the call.  W: [H * dim, rank], read once per 8 tokens.
+__global__ void __launch_bounds__(128) head_absorb_kernel(const float* __restrict__ q, const float* __restrict__ W, float* __restrict__ out, int T, int H, int dim, int rest,
+                                                          int rank) {
+    extern __shared__ float ha_sm[];
+    const int t0 = blockIdx.x * HP_TOK, h = blockIdx.y;
+    const int qs = dim + rest, os = rank + rest;
+    for (int i = threadIdx.x; i < HP_TOK * dim; i += 128) {
+        const int tt = i / dim, d = i - tt * dim;
+        ha_sm[i] = t0 + tt < T ? q[((int64_t)(t0 + tt) * H + h) * qs + d] : 0.0f;
+    }
+    __syncthreads();
+    for (int r = threadIdx.x; r < rank; r += 128) {
+        float acc[HP_TOK];
+#pragma unroll
+        for (int tt = 0; tt < HP_TOK; tt++) acc[tt] = 0.0f;
+        const float* wp = W + (int64_t)h * dim * rank + r;
+        for (int d = 0; d < dim; d++) {
+            const float wv = wp[(int64_t)d * rank];
+#pragma unroll
+            for (int tt = 0; tt < HP_TOK; tt++) acc[tt] = fmaf(ha_sm[tt * dim + d], wv, acc[tt]);
+        }
+#pragma unroll
+        for (int tt = 0; tt < HP_TOK; tt++)
+            if (t0 + tt < T) out[((int64_t)(t0 + tt) * H + h) * os + r] = acc[tt];
+    }
+    for (int i = threadIdx.x; i < HP_TOK * rest; i += 128) {
+        const int tt = i / rest, j = i - tt * rest;
+        if (t0 + tt < T) out[((int64_t)(t0 + tt) * H + h) * os + rank + j] = q[((int64_t)(t0 + tt) * H + h) * qs + dim + j];
+    }
+}
+extern "C" CC_API int cc_head_absorb(cc_device* dev, const cc_view* q, const cc_view* w, int32_t n_heads, int32_t dim, int32_t rest, cc_buf** out) {
+    SEQ_ENTER(dev, "head_absorb");
+    if (!out) return cc_fail(dev, CC_ERR_ARG, "head_absorb: out is NULL");
+    SEQ_F32(dev, q, "head_absorb q"); SEQ_F32(dev, w, "head_absorb w");
+    CC_REQUIRE(dev, q->ndim == 2 && w->ndim == 2 && n_heads > 0 && dim > 0 && rest >= 0 && q->shape[1] == (int64_t)n_heads * (dim + rest) && w->shape[0] == (int64_t)n_heads * dim,
+               "head_absorb: q must be [T, heads * (dim + rest)] and w [heads * dim, rank]");
+    const int64_t T = q->shape[0], rank = w->shape[1];
+    CC_REQUIRE(dev, (size_t)HP_TOK * dim * 4 <= 48 * 1024, "head_absorb: heads of %d do not fit shared memory", dim);
+    cc_buf* o = nullptr;
+    int rc = cc_new_activation(dev, T * n_heads * (rank + rest), CC_F32, false, &o);
+    if (rc) return rc;
+    *out = o;
+    if (T == 0) return CC_OK;
+    head_absorb_kernel<<<dim3((unsigned)((T + HP_TOK - 1) / HP_TOK), (unsigned)n_heads), 128, (size_t)HP_TOK * dim * 4, dev->stream>>>(fptr(q), fptr(w), (float*)o->base, (int)T,
+                                                                                                                                      n_heads, dim, rest, (int)rank);
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}
+// grid (ceil(T / 8), H, ceil(vdim / 4)): the CTA stages 8 tokens' x[t, h, :rank]; a warp owns one output column: lane-strided partial sums over
+// the rank, then the butterfly (one order per output).  W: [H * vdim, rank].
+__global__ void __launch_bounds__(128) head_expand_kernel(const float* __restrict__ x, const float* __restrict__ W, float* __restrict__ out, int T, int H, int rank, int vdim) {
+    extern __shared__ float he_sm[];
+    const int t0 = blockIdx.x * HP_TOK, h = blockIdx.y;
+    for (int i = threadIdx.x; i < HP_TOK * rank; i += 128) {
+        const int tt = i / rank, r = i - tt * rank;
+        he_sm[i] = t0 + tt < T ? x[((int64_t)(t0 + tt) * H + h) * rank + r] : 0.0f;
+    }
+    __syncthreads();
+    const int v = blockIdx.z * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (v >= vdim) return;
+    const float* wp = W + ((int64_t)h * vdim + v) * rank;
+    float acc[HP_TOK];
+#pragma unroll
+    for (int tt = 0; tt < HP_TOK; tt++) acc[tt] = 0.0f;
+    for (int r = lane; r < rank; r += 32) {
+        const float wv = wp[r];
+#pragma unroll
+        for (int tt = 0; tt < HP_TOK; tt++) acc[tt] = fmaf(he_sm[tt * rank + r], wv, acc[tt]);
+    }
+#pragma unroll
+    for (int tt = 0; tt < HP_TOK; tt++) {
+        const float s = warp_sum(acc[tt]);
+        if (lane == 0 && t0 + tt < T) out[((int64_t)(t0 + tt) * H + h) * vdim + v] = s;
+    }
+}
+extern "C" CC_API int cc_head_expand(cc_device* dev, const cc_view* x, const cc_view* w, int32_t n_heads, int32_t vdim, cc_buf** out) {
+    SEQ_ENTER(dev, "head_expand");
+    if (!out) return cc_fail(dev, CC_ERR_ARG, "head_expand: out is NULL");
+    SEQ_F32(dev, x, "head_expand x"); SEQ_F32(dev, w, "head_expand w");
+    CC_REQUIRE(dev, x->ndim == 2 && w->ndim == 2 && n_heads > 0 && vdim > 0 && w->shape[0] == (int64_t)n_heads * vdim && x->shape[1] == (int64_t)n_heads * w->shape[1],
+               "head_expand: x must be [T, heads * rank] and w [heads * vdim, rank]");
+    const int64_t T = x->shape[0], rank = w->shape[1];
+    const size_t smem = (size_t)HP_TOK * rank * 4;
+    CC_REQUIRE(dev, smem <= 160 * 1024, "head_expand: rank %lld does not fit shared memory", (long long)rank);
+    cc_buf* o = nullptr;
+    int rc = cc_new_activation(dev, T * n_heads * vdim, CC_F32, false, &o);
+    if (rc) return rc;
+    *out = o;
+    if (T == 0) return CC_OK;
+    if (smem > 48 * 1024) CC_CUDA(dev, cudaFuncSetAttribute(head_expand_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    head_expand_kernel<<<dim3((unsigned)((T + HP_TOK - 1) / HP_TOK), (unsigned)n_heads, (unsigned)((vdim + 3) / 4)), 128, smem, dev->stream>>>(fptr(x), fptr(w), (float*)o->base,
+                                                                                                                                               (int)T, n_heads, (int)rank, vdim);
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}
+
+// ---- PolyNorm ------------------------------------------------------------------------------------------------------------------------------
+// one CTA per row: thread-strided sums of z^2, z^4, z^6, a fixed tree over the 256 partial sums, then the weighted sum of the three unit powers
+__global__ void __launch_bounds__(256) poly_norm_kernel(float* __restrict__ z, const float* __restrict__ coef, int cols, float eps) {
+    __shared__ float red[3][8];
+    float* zr = z + (int64_t)blockIdx.x * cols;
+    float s2 = 0.0f, s4 = 0.0f, s6 = 0.0f;
+    for (int c = threadIdx.x; c < cols; c += 256) {
+        const float v = zr[c], v2 = v * v, v3 = v2 * v;
+        s2 += v2; s4 = fmaf(v2, v2, s4); s6 = fmaf(v3, v3, s6);
+    }
+    s2 = warp_sum(s2); s4 = warp_sum(s4); s6 = warp_sum(s6);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) { red[0][warp] = s2; red[1][warp] = s4; red[2][warp] = s6; }
+    __syncthreads();
+    float t2 = 0.0f, t4 = 0.0f, t6 = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) { t2 += red[0][w]; t4 += red[1][w]; t6 += red[2][w]; }
+    const float i1 = 1.0f / sqrtf(t2 / (float)cols + eps), i2 = 1.0f / sqrtf(t4 / (float)cols + eps), i3 = 1.0f / sqrtf(t6 / (float)cols + eps);
+    const float a = coef[0], b = coef[1], c3 = coef[2], e = coef[3];
+    for (int c = threadIdx.x; c < cols; c += 256) {
+        const float v = zr[c], v2 = v * v, v3 = v2 * v;
+        zr[c] = a * (v * i1) + b * (v2 * i2) + c3 * (v3 * i3) + e;
+    }
+}
+extern "C" CC_API int cc_poly_norm(cc_device* dev, const cc_view* z, const cc_view* coef, float eps) {
+    SEQ_ENTER(dev, "poly_norm");
+    SEQ_F32(dev, z, "poly_norm z"); SEQ_F32(dev, coef, "poly_norm coef");
+    CC_REQUIRE(dev, z->ndim == 2 && view_len(coef) == 4, "poly_norm: z must be [rows, cols] and coef hold 4 numbers");
+    if (z->shape[0] == 0) return CC_OK;
+    poly_norm_kernel<<<(unsigned)z->shape[0], 256, 0, dev->stream>>>(fptr(z), fptr(coef), (int)z->shape[1], eps);
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}
+
+// ---- gated sum of sublayer results into the residual stream -----------------------------------------------------------------------------------
+__global__ void gated_sum_kernel(float* __restrict__ dst, const float* __restrict__ y1, const float* __restrict__ g1, const float* __restrict__ b1, const float* __restrict__ y2,
+                                 const float* __restrict__ g2, const float* __restrict__ b2, int64_t n, int cols, int accumulate) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int c = (int)(i % cols);
+    float v = y1[i];
+    if (g1) v *= seq_sigmoid(g1[i] + (b1 ? b1[c] : 0.0f));
+    if (y2) {
+        float u = y2[i];
+        if (g2) u *= seq_sigmoid(g2[i] + (b2 ? b2[c] : 0.0f));
+        v += u;
+    }
+    dst[i] = accumulate ? dst[i] + v : v;
+}
+extern "C" CC_API int cc_gated_sum(cc_device* dev, const cc_view* dst, int32_t accumulate, const cc_view* y1, const cc_view* g1, const cc_view* b1, const cc_view* y2,
+                                   const cc_view* g2, const cc_view* b2) {
+    SEQ_ENTER(dev, "gated_sum");
+    SEQ_F32(dev, dst, "gated_sum dst"); SEQ_F32(dev, y1, "gated_sum y1");
+    CC_REQUIRE(dev, dst->ndim == 2, "gated_sum: dst must be [rows, cols]");
+    const int64_t n = view_len(dst), cols = dst->shape[1];
+    const cc_view* same[] = {y1, g1, y2, g2};
+    for (const cc_view* v : same)
+        if (v) { SEQ_F32(dev, v, "gated_sum operand"); CC_REQUIRE(dev, view_len(v) == n, "gated_sum: an operand has %lld elements, dst %lld", (long long)view_len(v), (long long)n); }
+    const cc_view* bias[] = {b1, b2};
+    for (const cc_view* v : bias)
+        if (v) { SEQ_F32(dev, v, "gated_sum bias"); CC_REQUIRE(dev, view_len(v) == cols, "gated_sum: a bias needs one number per column"); }
+    CC_REQUIRE(dev, (!b1 || g1) && (!b2 || g2) && (!g2 || y2), "gated_sum: a bias needs its gate, a gate its operand");
+    if (n == 0) return CC_OK;
+    gated_sum_kernel<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>(fptr(dst), fptr(y1), g1 ? fptr(g1) : nullptr, b1 ? fptr(b1) : nullptr, y2 ? fptr(y2) : nullptr,
+                                                                           g2 ? fptr(g2) : nullptr, b2 ? fptr(b2) : nullptr, n, (int)cols, accumulate);
     CC_LAUNCH_CHECK(dev);
     return CC_OK;
 }

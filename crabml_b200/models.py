@@ -46,3 +46,11 @@ def _load_zatorax(path, device, dtype="bfloat16", chunk=0, **_):
 
 
 register("Zatorax", _load_zatorax)
+
+
+def _load_meresun(path, device, dtype="bfloat16", chunk=0, max_tokens=0, **_):
+    from . import meresun
+    return meresun.load(path, device, dtype, chunk, max_tokens)
+
+
+register("Meresun", _load_meresun)

@@ -1,0 +1,35 @@
+"""Frequency tables for cc_rope_pairs / cc_latent_ring_append (include/crabml_seqops.h): one frequency per rotated pair and one factor
+on cos and sin.  The kernels multiply position and frequency in 32-bit; whatever a model does to its frequencies lives in the table."""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+
+
+def plain_table(dims: int, base: float):
+    """pair i turns by position * base^(-2 i / dims)"""
+    i = np.arange(dims // 2, dtype=np.float64)
+    return np.power(float(base), -2.0 * i / dims), 1.0
+
+
+def yarn_table(dims: int, base: float, factor: float, original: float, fast: float, slow: float):
+    """YaRN: pairs that turn more than `fast` times over the original context keep their frequency, pairs that turn less than `slow`
+    times have it divided by `factor`, a linear ramp over the pair index joins the two; cos and sin grow by 0.1 ln(factor) + 1."""
+    f, _ = plain_table(dims, base)
+
+    def pair_of(turns):                       # the (fractional) pair index that makes `turns` full turns over the original context
+        return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+    lo = max(math.floor(pair_of(fast)), 0)
+    hi = min(math.ceil(pair_of(slow)), dims - 1)
+    i = np.arange(dims // 2, dtype=np.float64)
+    ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    return f / factor * ramp + f * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
+
+
+def table_of(rot: dict):
+    """rot: {"dims", "base", optional "scaling": {"factor", "original", "fast", "slow"}} -> (float32 frequencies [dims / 2], factor)"""
+    dims, base = int(rot["dims"]), float(rot["base"])
+    sc = rot.get("scaling")
+    f, mag = yarn_table(dims, base, float(sc["factor"]), float(sc["original"]), float(sc["fast"]), float(sc["slow"])) if sc else plain_table(dims, base)
+    return f.astype(np.float32), float(mag)

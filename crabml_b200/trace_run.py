@@ -27,14 +27,14 @@ def main(argv=None):
     ap.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder the logits are written to")
-    ap.add_argument("--max-tokens", type=int, default=0, help="most tokens live requests hold at any time (state is per sequence and bounded; unused)")
+    ap.add_argument("--max-tokens", type=int, default=0, help="most tokens live requests hold at any time (sizes the cache of a layer that has no window; other state is bounded per sequence)")
     ap.add_argument("--chunk", type=int, default=0, help="longest run of tokens one pass takes (0: the runner's default)")
     a = ap.parse_args(argv)
 
     from . import models
     from .tensor import CudaTensorDevice
     device = CudaTensorDevice()
-    model = models.load_model(a.model, device, dtype=a.dtype, chunk=a.chunk)
+    model = models.load_model(a.model, device, dtype=a.dtype, chunk=a.chunk, max_tokens=a.max_tokens)
     if not hasattr(model, "step"):
         print(f"trace_run: architecture {models.architecture_of(a.model)!r} has no multi-sequence step interface", file=sys.stderr)
         return 3

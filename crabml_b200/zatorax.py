@@ -15,12 +15,13 @@ from __future__ import annotations
 import ctypes as C
 import json
 import os
-import struct
 
 import numpy as np
 
 from . import capi
 from .capi import CudaError, TensorError
+from .safetensors import bf16_to_f32, f32_to_bf16, read_safetensors, write_safetensors  # noqa: F401  (also this module's names)
+from .seqmodel import SeqModel
 from .tensor import CudaTensor, CudaTensorDevice
 
 ARCHITECTURE = "Zatorax"
@@ -91,50 +92,6 @@ def expected_tensors(conf: dict) -> dict:
     return t
 
 
-# ---- safetensors: 8-byte little-endian header length, JSON header (name -> dtype, shape, data_offsets), then the data ---------------
-def bf16_to_f32(u16: np.ndarray) -> np.ndarray:
-    return (u16.astype(np.uint32) << 16).view(np.float32)
-
-
-def f32_to_bf16(x: np.ndarray) -> np.ndarray:
-    """round to nearest even, as uint16 bit patterns"""
-    u = np.ascontiguousarray(x, np.float32).view(np.uint32)
-    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
-
-
-def read_safetensors(path: str) -> dict:
-    """-> ({name: ndarray}, names stored as bfloat16); bfloat16 tensors come back as their uint16 bit patterns."""
-    with open(path, "rb") as f:
-        (n,) = struct.unpack("<Q", f.read(8))
-        meta = json.loads(f.read(n))
-        data = f.read()
-    kinds = {"BF16": np.uint16, "F32": np.float32, "F16": np.float16, "I32": np.int32}
-    out, bf16 = {}, set()
-    for name, m in meta.items():
-        if name == "__metadata__":
-            continue
-        if m["dtype"] not in kinds:
-            raise TensorError(f"{name}: unsupported dtype {m['dtype']}")
-        a, b = m["data_offsets"]
-        out[name] = np.frombuffer(data[a:b], kinds[m["dtype"]]).reshape(m["shape"])
-        if m["dtype"] == "BF16":
-            bf16.add(name)
-    return out, bf16
-
-
-def write_safetensors(path: str, tensors: dict):
-    """tensors: {name: float32 ndarray}; stored as bfloat16 (used by tests and examples to make model folders)."""
-    meta, blobs, off = {}, [], 0
-    for name, a in tensors.items():
-        raw = f32_to_bf16(np.asarray(a, np.float32)).tobytes()
-        meta[name] = {"dtype": "BF16", "shape": list(np.asarray(a).shape), "data_offsets": [off, off + len(raw)]}
-        blobs.append(raw)
-        off += len(raw)
-    hdr = json.dumps(meta).encode()
-    with open(path, "wb") as f:
-        f.write(struct.pack("<Q", len(hdr)) + hdr + b"".join(blobs))
-
-
 def random_weights(conf: dict, seed: int = 0, scale: float = 1.0) -> dict:
     """Random weights of a config (float32 arrays whose values are exact in bfloat16), sized so that activations stay O(1)."""
     rng = np.random.default_rng(seed)
@@ -166,8 +123,8 @@ def random_weights(conf: dict, seed: int = 0, scale: float = 1.0) -> dict:
 
 
 # ---- the model on a device ------------------------------------------------------------------------------------------------------------
-class ZatoraxModel:
-    """Weights of one model on one device + its runner.  `weights`: {name: float32 ndarray} (values representable in bfloat16 when
+class ZatoraxModel(SeqModel):
+    """Weights of one model on one device + its runner (sequences, steps and generation: seqmodel.SeqModel).  `weights`: {name: float32 ndarray} (values representable in bfloat16 when
     dtype == "bfloat16") or the pair read_safetensors returns."""
 
     def __init__(self, device: CudaTensorDevice, conf: dict, weights, dtype: str = "bfloat16", chunk: int = 0):
@@ -257,50 +214,8 @@ class ZatoraxModel:
         if rc != capi.CC_OK:
             raise (TensorError if rc == capi.CC_ERR_TENSOR else CudaError)(f"czr_runner_create failed [{rc}]: {device.lib.czr_last_create_error().decode()}")
         self.handle = h
+        self.vocab = c["vocab"]
         self._keep = (lcs, lws)
-
-    # ---- sequences -----------------------------------------------------------------------------------------------------------------
-    def _check(self, rc):
-        if rc == capi.CC_OK:
-            return
-        msg = self.device.lib.czr_runner_last_error(self.handle).decode()
-        raise (TensorError if rc == capi.CC_ERR_TENSOR else CudaError)(msg)
-
-    def open(self) -> int:
-        s = C.c_int32(-1)
-        self._check(self.device.lib.czr_seq_open(self.handle, C.byref(s)))
-        return int(s.value)
-
-    def close_seq(self, slot: int):
-        self._check(self.device.lib.czr_seq_close(self.handle, int(slot)))
-
-    def seq_len(self, slot: int) -> int:
-        return int(self.device.lib.czr_seq_len(self.handle, int(slot)))
-
-    def stats(self) -> dict:
-        a = (C.c_int64 * 3)()
-        self._check(self.device.lib.czr_runner_stats(self.handle, a))
-        return {"slots": int(a[0]), "live": int(a[1]), "state_bytes_per_slot": int(a[2])}
-
-    def step(self, slot: int, tokens, want=()) -> np.ndarray:
-        """feeds the sequence's next tokens; -> logits [len(want), vocab] of the wanted places among them"""
-        toks = (C.c_int64 * len(tokens))(*[int(t) for t in tokens])
-        w = (C.c_int32 * max(1, len(want)))(*[int(i) for i in want])
-        out = np.zeros((len(want), self.conf["vocab"]), np.float32)
-        self._check(self.device.lib.czr_runner_step(self.handle, int(slot), toks, len(tokens), w, len(want), out.ctypes.data_as(C.c_void_p) if len(want) else None))
-        return out
-
-    def generate_greedy(self, slot: int, prompt, steps: int, eos: int = -1):
-        p = (C.c_int64 * len(prompt))(*[int(t) for t in prompt])
-        out = (C.c_int64 * max(1, steps))()
-        n = C.c_int32(0)
-        self._check(self.device.lib.czr_runner_generate_greedy(self.handle, int(slot), p, len(prompt), steps, eos, out, C.byref(n)))
-        return [int(out[i]) for i in range(n.value)]
-
-    def close(self):
-        if getattr(self, "handle", None):
-            self.device.lib.czr_runner_destroy(self.handle)
-            self.handle = None
 
 
 def load(path: str, device: CudaTensorDevice, dtype: str = "bfloat16", chunk: int = 0) -> ZatoraxModel:

@@ -21,7 +21,8 @@
 extern "C" {
 #endif
 
-enum cc_activation { CC_ACT_NONE = 0, CC_ACT_SILU = 1, CC_ACT_GELU_TANH = 2 };
+/* CC_ACT_SWISH: z * sigmoid(alpha * z) with alpha given beside it (cc_glu_params); the others take no constant */
+enum cc_activation { CC_ACT_NONE = 0, CC_ACT_SILU = 1, CC_ACT_GELU_TANH = 2, CC_ACT_SWISH = 3 };
 
 /* x (any shape) = 0 */
 CC_API int cc_tensor_zero(cc_device* dev, const cc_view* x);
@@ -33,6 +34,16 @@ CC_API int cc_rms_norm_gain(cc_device* dev, const cc_view* dst, const cc_view* y
 /* x[r, h, :] = x[r, h, :] / sqrt(mean(x[r, h, :]^2) + eps) * w[:] * act(gate[r, h, :]) ; x, gate: [rows, heads * head_size], w: [head_size] */
 CC_API int cc_gated_head_rms_norm(cc_device* dev, const cc_view* x, const cc_view* gate, const cc_view* w, int32_t head_size, float eps,
                                   int32_t gate_act);
+/* dst[r] = x[r] with every one of `groups` equal consecutive parts of the row divided by its own sqrt(mean(part^2) + eps), times w[:]
+ * (w: cols numbers).  groups = 1 is the plain weighted RMS norm.  dst may be x. */
+CC_API int cc_group_rms_norm(cc_device* dev, const cc_view* dst, const cc_view* x, const cc_view* w, int32_t groups, float eps);
+/* PolyNorm, in place on z [rows, cols]: z <- a N(z) + b N(z^2) + c N(z^3) + e with coef = {a, b, c, e}; powers are taken element by
+ * element and N divides the row by its root mean square, N(y) = y / sqrt(mean(y^2) + eps). */
+CC_API int cc_poly_norm(cc_device* dev, const cc_view* z, const cc_view* coef, float eps);
+/* dst = (accumulate ? dst : 0) + y1 * sigmoid(g1 + b1) + y2 * sigmoid(g2 + b2) ; all [rows, cols] but the biases [cols].  g1 / g2 NULL:
+ * that operand is not gated; y2 NULL: one operand.  The residual update of a block whose sublayers run side by side on one input. */
+CC_API int cc_gated_sum(cc_device* dev, const cc_view* dst, int32_t accumulate, const cc_view* y1, const cc_view* g1, const cc_view* b1, const cc_view* y2,
+                        const cc_view* g2, const cc_view* b2);
 /* gate = act(gate) * up, elementwise (the inner step of a gated feed-forward, exact 32-bit activation) */
 CC_API int cc_glu_inplace(cc_device* dev, const cc_view* gate, const cc_view* up, int32_t act);
 
@@ -69,6 +80,35 @@ CC_API int cc_window_attention(cc_device* dev, const cc_view* q, const cc_view* 
                                int64_t pos0, int32_t n_heads, int32_t n_kv, int32_t dk, int32_t dv, int32_t window, float scale,
                                const cc_view* r1, const cc_view* r2, cc_buf** out);
 
+/* cc_window_attention with two more options.  sink ([n_heads] or NULL): the softmax denominator also holds exp(sink[h]), a key that has
+ * no value and whose score is sink[h] as it stands.  vring == NULL: a key row's first dv columns are its value (dv <= dk): a cache of
+ * latent rows that serve as keys and as values. */
+CC_API int cc_window_attention_sink(cc_device* dev, const cc_view* q, const cc_view* q_norm_w, float eps, const cc_view* kring, const cc_view* vring,
+                                    int64_t pos0, int32_t n_heads, int32_t n_kv, int32_t dk, int32_t dv, int32_t window, float scale,
+                                    const cc_view* r1, const cc_view* r2, const cc_view* sink, cc_buf** out);
+
+/* ---- rotary positions from a frequency table ----------------------------------------------------------------------------------- */
+/* x: [T, n_heads * head_size], rows are positions pos0 .. ; freq: [P] one frequency per pair.  In every head the columns
+ * offset + 2i and offset + 2i + 1 (i < P) are rotated by the angle a = position * freq[i] (a 32-bit product):
+ *   (u, v) <- ((u cos a - v sin a) * mag, (v cos a + u sin a) * mag) ; all other columns stay.  In place.
+ * The table carries whatever scaling of the frequencies a model uses (crabml_b200/rotary.py builds plain and YaRN tables). */
+CC_API int cc_rope_pairs(cc_device* dev, const cc_view* x, int32_t n_heads, int32_t head_size, int32_t offset, const cc_view* freq, float mag, int64_t pos0);
+
+/* ---- latent key/value cache --------------------------------------------------------------------------------------------------- */
+/* A cache row is [c | r]: c, `rank` numbers from which keys and values of all heads derive, and r, a rotated key part that all heads
+ * share.  Appends T rows ckv [T, cols] at positions pos0 .. to ring [R, cols] (position p lives in row p % R): the first `rank` columns
+ * are RMS-normalised (eps) and multiplied by norm_w ([rank], NULL = 1), the next 2 * P columns are rotated like cc_rope_pairs does
+ * (freq [P], NULL = none), any further column is copied. */
+CC_API int cc_latent_ring_append(cc_device* dev, const cc_view* ring, const cc_view* ckv, const cc_view* norm_w, float eps, int32_t rank, const cc_view* freq,
+                                 float mag, int64_t pos0);
+/* Folds a per-head key up-projection into the query, so that scores are taken against the latent rows themselves:
+ *   out[t, h] = [ W_h^T q[t, h, :dim] | q[t, h, dim:] ]     q: [T, heads * (dim + rest)], w: [heads * dim, rank] (W_h = rows h*dim ..), F32
+ * out: [T, heads * (rank + rest)].  (q_h . (W_h c) = (W_h^T q_h) . c) */
+CC_API int cc_head_absorb(cc_device* dev, const cc_view* q, const cc_view* w, int32_t n_heads, int32_t dim, int32_t rest, cc_buf** out);
+/* The per-head value up-projection of an attention result over latent rows: out[t, h] = W_h x[t, h]
+ *   x: [T, heads * rank], w: [heads * vdim, rank] F32; out: [T, heads * vdim]. */
+CC_API int cc_head_expand(cc_device* dev, const cc_view* x, const cc_view* w, int32_t n_heads, int32_t vdim, cc_buf** out);
+
 /* ---- routed feed-forward ---------------------------------------------------------------------------------------------------- */
 /* x: [T, D]; router_w: [E, D] F32; correction: [E] or NULL.  s = softmax(router_w x) over all experts (32-bit).  Choice score =
  * s + correction.  Experts form n_groups equal groups of neighbours; a group's score is its largest choice score; only experts of the
@@ -77,6 +117,26 @@ CC_API int cc_window_attention(cc_device* dev, const cc_view* q, const cc_view* 
  * ids_out: I32 [T, top]; weights_out: F32 [T, top]. */
 CC_API int cc_moe_route(cc_device* dev, const cc_view* x, const cc_view* router_w, const cc_view* correction, int32_t top, int32_t n_groups,
                         int32_t keep_groups, int32_t renormalise, cc_buf** ids_out, cc_buf** weights_out);
+/* cc_moe_route with every constant of the choice as a parameter. */
+enum cc_route_score { CC_ROUTE_SOFTMAX = 0, CC_ROUTE_SIGMOID = 1 };
+typedef struct cc_route_params {
+    int32_t score;               /* CC_ROUTE_SOFTMAX: s = softmax over all experts; CC_ROUTE_SIGMOID: s = sigmoid, expert by expert */
+    int32_t top, n_groups, keep_groups;
+    int32_t group_top;           /* a group's score is the sum of its group_top largest choice scores (1: its largest) */
+    int32_t renormalise;         /* != 0: the chosen weights are divided by (their sum + renorm_eps) */
+    float renorm_eps;
+} cc_route_params;
+CC_API int cc_moe_route_ex(cc_device* dev, const cc_view* x, const cc_view* router_w, const cc_view* correction, const cc_route_params* params,
+                           cc_buf** ids_out, cc_buf** weights_out);
+/* the gated unit of an expert: act(min(g, limit)) * (clamp(u, -limit, limit) + up_shift); limit <= 0: nothing is clamped */
+typedef struct cc_glu_params {
+    int32_t act;                 /* cc_activation */
+    float alpha;                 /* CC_ACT_SWISH only */
+    float limit, up_shift;
+} cc_glu_params;
+/* cc_moe_experts with the gated unit's constants as parameters (cc_moe_experts = {act, 1, 0, 0}) */
+CC_API int cc_moe_experts_glu(cc_device* dev, const cc_view* x, const cc_view* ids, const cc_view* weights, const cc_view* w_gate, const cc_view* w_up,
+                              const cc_view* w_down, int32_t n_experts, int32_t ff, const cc_glu_params* glu, cc_buf** out);
 /* out[t] = sum_s weights[t, s] * W_down[ids[t, s]] (act(W_gate[ids[t, s]] x[t]) * (W_up[ids[t, s]] x[t]))
  * w_gate, w_up: [E * ff, D]; w_down: [E * D, ff] (expert-major stacks; F32 or BF16).  out: [T, D]. */
 CC_API int cc_moe_experts(cc_device* dev, const cc_view* x, const cc_view* ids, const cc_view* weights, const cc_view* w_gate, const cc_view* w_up,

@@ -14,6 +14,7 @@
 #define CRABML_ZATORAX_H
 
 #include "crabml_seqops.h"
+#include "crabml_seqrunner.h"
 
 #ifdef __cplusplus
 extern "C" {
@@ -52,7 +53,8 @@ typedef struct czr_layer_weights {
     cc_buf *s_gate, *s_up, *s_down;                                   /* shared expert */
 } czr_layer_weights;
 
-typedef struct czr_runner czr_runner;
+/* a Zatorax runner is a sequence runner (crabml_seqrunner.h); the czr_ functions below the creation are the csr_ ones under their older names */
+typedef csr_runner czr_runner;
 
 CC_API int czr_runner_create(cc_device* dev, const czr_config* conf, const czr_layer_config* layers, const czr_layer_weights* weights, cc_buf* embed,
                              cc_buf* final_norm, cc_buf* head, czr_runner** out);
