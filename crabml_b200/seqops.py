@@ -74,3 +74,64 @@ def moe_experts(x, ids, weights, w_gate, w_up, w_down, n_experts, ff, act=capi.A
     x.device.check(x.device.lib.cc_moe_experts(x.device.handle, _v(x), _v(ids), _v(weights), _v(w_gate), _v(w_up), _v(w_down), int(n_experts), int(ff), int(act),
                                                C.byref(h)))
     return _new(x.device, h, list(x.shape()))
+
+
+def group_rms_norm(x, w, groups, eps, dst=None):
+    dst = dst if dst is not None else type(x).alloc(x.shape(), capi.F32, x.device)
+    x.device.check(x.device.lib.cc_group_rms_norm(x.device.handle, _v(dst), _v(x), _v(w), int(groups), float(eps)))
+    return dst
+
+
+def poly_norm(z, coef, eps):
+    z.device.check(z.device.lib.cc_poly_norm(z.device.handle, _v(z), _v(coef), float(eps)))
+    return z
+
+
+def gated_sum(dst, y1, g1=None, b1=None, y2=None, g2=None, b2=None, accumulate=True):
+    dst.device.check(dst.device.lib.cc_gated_sum(dst.device.handle, _v(dst), int(accumulate), _v(y1), _v(g1), _v(b1), _v(y2), _v(g2), _v(b2)))
+    return dst
+
+
+def rope_pairs(x, n_heads, head_size, offset, freq, mag, pos0):
+    x.device.check(x.device.lib.cc_rope_pairs(x.device.handle, _v(x), int(n_heads), int(head_size), int(offset), _v(freq), float(mag), int(pos0)))
+    return x
+
+
+def latent_ring_append(ring, ckv, norm_w, eps, rank, freq, mag, pos0):
+    ring.device.check(ring.device.lib.cc_latent_ring_append(ring.device.handle, _v(ring), _v(ckv), _v(norm_w), float(eps), int(rank), _v(freq), float(mag), int(pos0)))
+
+
+def head_absorb(q, w, n_heads, dim, rest):
+    h = C.c_void_p()
+    q.device.check(q.device.lib.cc_head_absorb(q.device.handle, _v(q), _v(w), int(n_heads), int(dim), int(rest), C.byref(h)))
+    return _new(q.device, h, [q.shape()[0], n_heads * (w.shape()[1] + rest)])
+
+
+def head_expand(x, w, n_heads, vdim):
+    h = C.c_void_p()
+    x.device.check(x.device.lib.cc_head_expand(x.device.handle, _v(x), _v(w), int(n_heads), int(vdim), C.byref(h)))
+    return _new(x.device, h, [x.shape()[0], n_heads * vdim])
+
+
+def window_attention_sink(q, kring, vring, pos0, n_heads, n_kv, dk, dv, window, scale, sink=None, q_norm_w=None, eps=0.0, r1=None, r2=None):
+    """vring None: a key row's first dv columns are its value"""
+    h = C.c_void_p()
+    q.device.check(q.device.lib.cc_window_attention_sink(q.device.handle, _v(q), _v(q_norm_w), float(eps), _v(kring), _v(vring), int(pos0), n_heads, n_kv, dk, dv,
+                                                         int(window), float(scale), _v(r1), _v(r2), _v(sink), C.byref(h)))
+    return _new(q.device, h, [q.shape()[0], n_heads * dv])
+
+
+def moe_route_ex(x, router_w, correction, top, n_groups=1, keep_groups=1, score=capi.ROUTE_SOFTMAX, group_top=1, renormalise=False, renorm_eps=0.0):
+    hi, hw = C.c_void_p(), C.c_void_p()
+    rp = capi.cc_route_params(int(score), int(top), int(n_groups), int(keep_groups), int(group_top), int(renormalise), float(renorm_eps))
+    x.device.check(x.device.lib.cc_moe_route_ex(x.device.handle, _v(x), _v(router_w), _v(correction), C.byref(rp), C.byref(hi), C.byref(hw)))
+    T = x.shape()[0]
+    return _new(x.device, hi, [T, top]), _new(x.device, hw, [T, top])
+
+
+def moe_experts_glu(x, ids, weights, w_gate, w_up, w_down, n_experts, ff, act=capi.ACT_SILU, alpha=1.0, limit=0.0, up_shift=0.0):
+    h = C.c_void_p()
+    gp = capi.cc_glu_params(int(act), float(alpha), float(limit), float(up_shift))
+    x.device.check(x.device.lib.cc_moe_experts_glu(x.device.handle, _v(x), _v(ids), _v(weights), _v(w_gate), _v(w_up), _v(w_down), int(n_experts), int(ff), C.byref(gp),
+                                                   C.byref(h)))
+    return _new(x.device, h, list(x.shape()))
