@@ -39,6 +39,9 @@ WORKLOADS = {
     # the Zatorax family at layer sizes of a real model (random weights), beside a llama stack of equal size; see run_zatorax
     "zatorax-w1024": ("ZATORAX", "BF16", "BF16"),
     "zatorax-w2048": ("ZATORAX", "BF16", "BF16"),
+    # the Meresun family at the same layer sizes, beside the Zatorax stack of equal width and depth; see run_meresun
+    "meresun-w1024": ("MERESUN", "BF16", "BF16"),
+    "meresun-w2048": ("MERESUN", "BF16", "BF16"),
 }
 # dram bytes per megakernel launch from the committed ncu --set full capture (profiles/); None until captured
 TRAFFIC = {("llama2-7b-q8_0", 1): 7040893000 + 49879296}     # profiles/r02p_mega_ring_q8_0_ncu_raw.csv (mega_ring_kernel: dram__bytes_read.sum + dram__bytes_write.sum)
@@ -548,24 +551,9 @@ def zatorax_bench_config(width: int, n_layers: int = 4, vocab: int = 32000):
     return {"architecture": "Zatorax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": layers}
 
 
-def run_zatorax(args, rank, world, local_rank):
-    """Prefill and decode throughput of the Zatorax family at real layer sizes, beside the closest existing model -- a llama stack of the
-    same width, depth, head layout and ACTIVE feed-forward width (Q8_0 weights, its serving format) -- through each family's runner.
-    A prefill step = one `--prefill-tokens` prompt through model.step (logits of the last position read back); a decode step = one token."""
-    from crabml_b200 import CudaTensorDevice, zatorax
-    from crabml_b200 import runner as R
-    if rank != 0:
-        return
-    width = int(args.workload.split("-w")[1])
-    conf = zatorax.parse_config(zatorax_bench_config(width))
-    Tp, K, W = args.prefill_tokens, args.steps, args.warmup
-    rng = np.random.default_rng(SEED)
-    prompt = [int(v) for v in rng.integers(0, conf["vocab"], Tp)]
-    sampler = ClockSampler(local_rank); sampler.start()
-    out = {}
-    dev = CudaTensorDevice(local_rank, lazy=0)
-    model = zatorax.ZatoraxModel(dev, conf, zatorax.random_weights(conf, SEED), "bfloat16", chunk=args.zatorax_chunk)
-    params = sum(int(np.prod(sh)) if sh else 1 for sh in zatorax.expected_tensors(conf).values())
+def measure_seq_model(dev, model, prompt, K, W, params):
+    """prefill and decode of one slot-based model (seqmodel.SeqModel) through its step function; device time and wall time"""
+    Tp = len(prompt)
     l0 = dev.launch_count()
     for rep in range(2):                                             # first pass warms up (tensor maps, pool, function attributes)
         slot = model.open()
@@ -585,9 +573,74 @@ def run_zatorax(args, rank, world, local_rank):
         tok = int(np.argmax(lg[0]))
     dec_ms = dev.timer_end(); dec_wall = (time.perf_counter() - t0) * 1e3
     dec_launches = dev.launch_count() - l0
-    out["zatorax"] = {"params": params, "prefill_tok_s": Tp / (pre_ms * 1e-3), "prefill_ms": pre_ms, "prefill_wall_ms": pre_wall, "prefill_launches": int(pre_launches),
-                      "decode_tok_s": K / (dec_ms * 1e-3), "decode_ms_per_token": dec_ms / K, "decode_wall_ms_per_token": dec_wall / K,
-                      "decode_launches_per_token": dec_launches / K, "state": model.stats()}
+    return {"params": params, "prefill_tok_s": Tp / (pre_ms * 1e-3), "prefill_ms": pre_ms, "prefill_wall_ms": pre_wall, "prefill_launches": int(pre_launches),
+            "decode_tok_s": K / (dec_ms * 1e-3), "decode_ms_per_token": dec_ms / K, "decode_wall_ms_per_token": dec_wall / K,
+            "decode_launches_per_token": dec_launches / K, "state": model.stats()}
+
+
+def meresun_bench_config(width: int, vocab: int = 32000):
+    """four layers (dense, routed, dense, routed), each run once, so that depth and active feed-forward width (3 x width per token) equal
+    the Zatorax stack's; 128 + 64 wide query heads over a latent of 512, window 1024, 16 experts of 3/4 width (top 4 of the best 2 of 4 groups)"""
+    H = width // 128
+    mixer = {"heads": H, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": 3 * width // 4, "kv_rank": 512, "mask": {"size": 1024}, "scale": 192 ** -0.5,
+             "rot": {"dims": 64, "base": 10000.0, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    dense = {"kind": "dense", "ff": 3 * width}
+    moe = {"kind": "moe", "expert": {"ff": 3 * width // 4, "limit": 7.0}, "router": {"experts": 16, "top": 4, "groups": {"count": 4, "keep": 2}}}
+    layers = [{"type": "latent_attention", "mixer": mixer, "mlp": m} for m in (dense, moe, dense, moe)]
+    return {"architecture": "Meresun", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6, "groups": 4}, "token_side": {"dim": 64},
+            "loop": {"start": 0, "stop": 0, "times": 1}, "layers": layers}
+
+
+def run_meresun(args, rank, world, local_rank):
+    """Prefill and decode throughput of the Meresun family at real layer sizes, beside the closest existing model -- the Zatorax stack of
+    the same width, depth and active feed-forward width (run_zatorax's configuration) -- through the same step function and slots."""
+    from crabml_b200 import CudaTensorDevice, meresun, zatorax
+    if rank != 0:
+        return
+    width = int(args.workload.split("-w")[1])
+    Tp, K, W = args.prefill_tokens, args.steps, args.warmup
+    rng = np.random.default_rng(SEED)
+    prompt = [int(v) for v in rng.integers(0, 32000, Tp)]
+    sampler = ClockSampler(local_rank); sampler.start()
+    out = {}
+    for name, mod, cls, raw in (("meresun", meresun, "MeresunModel", meresun_bench_config(width)), ("zatorax", zatorax, "ZatoraxModel", zatorax_bench_config(width))):
+        conf = mod.parse_config(raw)
+        dev = CudaTensorDevice(local_rank, lazy=0)
+        model = getattr(mod, cls)(dev, conf, mod.random_weights(conf, SEED), "bfloat16", chunk=args.zatorax_chunk)
+        params = sum(int(np.prod(sh)) if sh else 1 for sh in mod.expected_tensors(conf).values())
+        out[name] = measure_seq_model(dev, model, prompt, K, W, params)
+        model.close(); dev.close()
+    clocks = sampler.stop()
+    z = out["meresun"]
+    line = {"metric": "decode_tokens_per_s", "value": z["decode_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": z["decode_ms_per_token"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 matrices and product inputs, f32 everything else", "data": "synthetic",
+            "config": {"workload": args.workload, "model": meresun_bench_config(width), "prefill_tokens": Tp, "chunk": args.zatorax_chunk,
+                       "closest_model": {"family": "zatorax", "model": zatorax_bench_config(width)}},
+            "e2e": {"value": 1e3 / z["decode_wall_ms_per_token"], "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 32000 * 4},
+            "gpu_launches": int(z["decode_launches_per_token"] * K), "detail": out, "clocks": clocks}
+    print(json.dumps(line))
+
+
+def run_zatorax(args, rank, world, local_rank):
+    """Prefill and decode throughput of the Zatorax family at real layer sizes, beside the closest existing model -- a llama stack of the
+    same width, depth, head layout and ACTIVE feed-forward width (Q8_0 weights, its serving format) -- through each family's runner.
+    A prefill step = one `--prefill-tokens` prompt through model.step (logits of the last position read back); a decode step = one token."""
+    from crabml_b200 import CudaTensorDevice, zatorax
+    from crabml_b200 import runner as R
+    if rank != 0:
+        return
+    width = int(args.workload.split("-w")[1])
+    conf = zatorax.parse_config(zatorax_bench_config(width))
+    Tp, K, W = args.prefill_tokens, args.steps, args.warmup
+    rng = np.random.default_rng(SEED)
+    prompt = [int(v) for v in rng.integers(0, conf["vocab"], Tp)]
+    sampler = ClockSampler(local_rank); sampler.start()
+    out = {}
+    dev = CudaTensorDevice(local_rank, lazy=0)
+    model = zatorax.ZatoraxModel(dev, conf, zatorax.random_weights(conf, SEED), "bfloat16", chunk=args.zatorax_chunk)
+    params = sum(int(np.prod(sh)) if sh else 1 for sh in zatorax.expected_tensors(conf).values())
+    out["zatorax"] = measure_seq_model(dev, model, prompt, K, W, params)
+    dec_launches = out["zatorax"]["decode_launches_per_token"] * K
     model.close(); dev.close()
     # the closest existing model at equal size
     H = width // 128
@@ -645,7 +698,7 @@ def main():
     ap.add_argument("--no-also", action="store_true", help="skip the second (Q4_0) measurement of the default run")
     ap.add_argument("--multi", default="sharded", choices=["sharded", "replicas"], help="N > 1: shard one token stream (strong scaling, default) or run N independent replicas")
     ap.add_argument("--comm", default="p2p", choices=["p2p", "nccl"], help="exchange transport of the sharded path: one-shot NVLink peer stores (default) or the NCCL baseline")
-    ap.add_argument("--zatorax-chunk", type=int, default=512, help="zatorax workloads: longest run of prompt tokens one pass takes")
+    ap.add_argument("--zatorax-chunk", type=int, default=512, help="zatorax / meresun workloads: longest run of prompt tokens one pass takes")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -654,6 +707,8 @@ def main():
         run_reference(args, rank, world)
     elif args.workload.startswith("zatorax-"):
         run_zatorax(args, rank, world, local_rank)
+    elif args.workload.startswith("meresun-"):
+        run_meresun(args, rank, world, local_rank)
     elif args.workload.endswith("-prefill"):
         run_prefill(args, rank, world, local_rank)
     else:

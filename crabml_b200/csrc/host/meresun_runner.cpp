@@ -3,8 +3,10 @@
 // in which order the tensor ops run.  Slots, step and greedy generation are the shared ones of seq_runner.hpp.
 //
 //   run:     h = group_norm(x) ; x += mixer(h) * sigmoid(W_g1 h + b1) + ff(h) * sigmoid(W_g2 h + b2) ; x += token_side(x, token)
-//   mixer:   c_q = norm(W_dq h) ; q = W_uq c_q, rotated part turned ; row [norm(c) | turned r] of W_dkv h into the run's ring ;
-//            q folded through W_uk ; windowed softmax with a sink over the ring's rows ; result through W_uv per head ; W_o
+//   mixer:   c_q = norm(W_dq h) ; q = W_uq c_q, rotated part turned ; row [norm(c) | turned r] of W_dkv h into the run's ring ; then
+//            few rows (decoding): q folded through W_uk ; windowed softmax with a sink over the ring's rows ; result through W_uv per head
+//            many rows (prompts): keys [W_uk c | r] and values W_uv c of the ring's rows as dense products ; the same attention per head
+//            ; W_o
 //   ff:      W_down PolyNorm(W_up h)   or   router -> top experts, weighted sum
 #include <cmath>
 #include <string>
@@ -20,7 +22,7 @@ namespace {
 
 struct Layer {
     cmr_layer_config c{};
-    CudaTensor norm1, dq, dq_norm, uq, dkv, dkv_norm, uk, uv, sink, rot_freq, o, rg1, rg1_b, rg2, rg2_b, up, down, act, router, correction, e_gate, e_up, e_down, side_table,
+    CudaTensor norm1, dq, dq_norm, uq, dkv, dkv_norm, uk, uv, uk_t, uv_f32, sink, rot_freq, o, rg1, rg1_b, rg2, rg2_b, up, down, act, router, correction, e_gate, e_up, e_down, side_table,
         side_gate, side_proj, side_norm;
     int64_t ring = 0;            // rows of the latent cache of one run of this layer
 };
@@ -81,19 +83,38 @@ struct Runner : csr_runner {
         cc_view qv = q.view();
         if (freq) check(cc_rope_pairs(dev, &qv, c.heads, c.dim + c.rot_dim, c.dim, freq, c.rot_mag, pos0));
         cc_buf* b = nullptr;
-        cc_view ukv = L.uk.view();
-        check(cc_head_absorb(dev, &qv, &ukv, c.heads, c.dim, c.rot_dim, &b));
-        CudaTensor ql = adopt(b, {n, (int64_t)c.heads * (c.kv_rank + c.rot_dim)});
-        // all heads read the one cached row per position: keys are whole rows, values their first kv_rank columns
-        cc_view qlv = ql.view(), rv = ring.view(), sk{};
-        b = nullptr;
-        check(cc_window_attention_sink(dev, &qlv, nullptr, 0.0f, &rv, nullptr, pos0, c.heads, 1, c.kv_rank + c.rot_dim, c.kv_rank, c.window, c.scale, nullptr, nullptr,
-                                       opt(L.sink, sk), &b));
-        CudaTensor ol = adopt(b, {n, (int64_t)c.heads * c.kv_rank});
-        cc_view olv = ol.view(), uvv = L.uv.view();
-        b = nullptr;
-        check(cc_head_expand(dev, &olv, &uvv, c.heads, c.vdim, &b));
-        CudaTensor o = adopt(b, {n, (int64_t)c.heads * c.vdim});
+        cc_view rv = ring.view(), sk{};
+        CudaTensor o;
+        if (n * c.heads > 64) {
+            // many rows: expand the cached rows once for all queries of the pass.  The expansion keeps the ring's row order (position p in
+            // row p % ring), so the attention reads it like the ring itself; rows no token has written yet are never visible.
+            const int64_t rows = std::min<int64_t>(L.ring, pos0 + n);
+            const int64_t cols = (int64_t)c.kv_rank + c.rot_dim;
+            CudaTensor lat = CudaTensor(ring).with_strider(crabml::TensorStrider({rows, c.kv_rank}, {cols, 1})).contiguous();
+            CudaTensor kp = L.uk.matmul_vec(lat), v = L.uv.matmul_vec(lat);
+            cc_view kpv = kp.view(), vv = v.view();
+            check(cc_head_concat_shared(dev, &kpv, &rv, c.heads, c.kv_rank, c.rot_dim, &b));
+            CudaTensor keys = adopt(b, {rows, (int64_t)c.heads * (c.dim + c.rot_dim)});
+            cc_view kv = keys.view();
+            b = nullptr;
+            check(cc_window_attention_sink(dev, &qv, nullptr, 0.0f, &kv, &vv, pos0, c.heads, c.heads, c.dim + c.rot_dim, c.vdim, c.window, c.scale, nullptr, nullptr,
+                                           opt(L.sink, sk), &b));
+            o = adopt(b, {n, (int64_t)c.heads * c.vdim});
+        } else {
+            // few rows: all heads read the one cached row per position; keys are whole rows, values their first kv_rank columns
+            cc_view ukv = L.uk_t.view();
+            check(cc_head_project(dev, &qv, &ukv, c.heads, c.rot_dim, &b));
+            CudaTensor ql = adopt(b, {n, (int64_t)c.heads * (c.kv_rank + c.rot_dim)});
+            cc_view qlv = ql.view();
+            b = nullptr;
+            check(cc_window_attention_sink(dev, &qlv, nullptr, 0.0f, &rv, nullptr, pos0, c.heads, 1, c.kv_rank + c.rot_dim, c.kv_rank, c.window, c.scale, nullptr, nullptr,
+                                           opt(L.sink, sk), &b));
+            CudaTensor ol = adopt(b, {n, (int64_t)c.heads * c.kv_rank});
+            cc_view olv = ol.view(), uvv = L.uv_f32.view();
+            b = nullptr;
+            check(cc_head_project(dev, &olv, &uvv, c.heads, 0, &b));
+            o = adopt(b, {n, (int64_t)c.heads * c.vdim});
+        }
         return L.o.matmul_vec(o);
     }
 
@@ -203,6 +224,7 @@ extern "C" CC_API int cmr_runner_create(cc_device* dev, const cmr_config* conf, 
             L.dq = need(w.dq, "mix.dq", {c.q_rank, D}); L.dq_norm = need(w.dq_norm, "mix.dq.norm", {c.q_rank}); L.uq = need(w.uq, "mix.uq", {c.heads * qh, c.q_rank});
             L.dkv = need(w.dkv, "mix.dkv", {(int64_t)c.kv_rank + c.rot_dim, D}); L.dkv_norm = need(w.dkv_norm, "mix.dkv.norm", {c.kv_rank});
             L.uk = need(w.uk, "mix.uk", {(int64_t)c.heads * c.dim, c.kv_rank}); L.uv = need(w.uv, "mix.uv", {hv, c.kv_rank});
+            L.uk_t = need(w.uk_t, "mix.uk (per head transposed)", {(int64_t)c.heads * c.kv_rank, c.dim}); L.uv_f32 = need(w.uv_f32, "mix.uv (F32)", {hv, c.kv_rank});
             L.o = need(w.o, "mix.o", {D, hv});
             L.sink = maybe(w.sink, {c.heads});
             if (w.rot_freq) {
@@ -210,7 +232,7 @@ extern "C" CC_API int cmr_runner_create(cc_device* dev, const cmr_config* conf, 
                 if (2 * pairs > c.rot_dim) throw TensorError(at + "more rotated pairs than the rotated part holds");
                 L.rot_freq = CudaTensor::wrap(dev, w.rot_freq, {pairs});
             }
-            if (L.uk.dtype() != CC_F32 || L.uv.dtype() != CC_F32) throw TensorError(at + "mix.uk / mix.uv must be F32: they enter the 32-bit scores and sums");
+            if (L.uk_t.dtype() != CC_F32 || L.uv_f32.dtype() != CC_F32) throw TensorError(at + "the folded forms of mix.uk / mix.uv must be F32: they enter the 32-bit scores and sums");
             L.rg1 = maybe(w.rg1, {D, D}); L.rg1_b = maybe(w.rg1_b, {D}); L.rg2 = maybe(w.rg2, {D, D}); L.rg2_b = maybe(w.rg2_b, {D});
             if ((L.rg1_b.valid() && !L.rg1.valid()) || (L.rg2_b.valid() && !L.rg2.valid())) throw TensorError(at + "a gate's bias without the gate");
             if (c.ff_kind == CMR_FF_DENSE) {

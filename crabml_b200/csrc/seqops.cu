@@ -507,6 +507,33 @@ __global__ void __launch_bounds__(WA_THREADS) wa_scores_kernel(const float* __re
         }
     }
 }
+// few rows (decoding): grid (ceil(keys / 8), T, G), 256 threads.  The CTA stages the R queries of (token, key/value head); a warp owns one
+// visible key and takes its dot product with each of them: lane-strided partial sums, then the butterfly.  The key row is read once for all
+// R heads, and the keys spread over the whole device however few rows the call has.
+__global__ void __launch_bounds__(256) wa_scores_row_kernel(const float* __restrict__ q, const float* __restrict__ kring, float* __restrict__ S, WaGeom g, float scale,
+                                                            const float* __restrict__ r1, const float* __restrict__ r2) {
+    extern __shared__ float wsr_sm[];             // [R][dk]
+    const int t = blockIdx.y, kvh = blockIdx.z;
+    const int64_t i = g.pos0 + t, lo = wa_lo(g, i);
+    for (int e = threadIdx.x; e < g.R * g.dk; e += 256) wsr_sm[e] = q[((int64_t)t * g.H + kvh * g.R) * g.dk + e];
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int64_t j = lo + (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (j > i) return;
+    const float* kr = kring + (j % g.ring) * g.krs + kvh * g.dk;
+    for (int hr = 0; hr < g.R; hr++) {
+        const float* qh = wsr_sm + hr * g.dk;
+        float acc = 0.0f;
+        for (int d = lane; d < g.dk; d += 32) acc = fmaf(qh[d], kr[d], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) {
+            const int h = kvh * g.R + hr;
+            float sc = acc * scale;
+            if (r1) sc -= r1[h] * log1pf(r2[h] * (float)(i - j));
+            S[((int64_t)t * g.H + h) * g.cap + (j - lo)] = sc;
+        }
+    }
+}
 // one warp per row
 // sink != NULL: the denominator also holds exp(sink[head]), a key without a value whose score is sink[head] as it stands (no scale)
 __global__ void wa_softmax_kernel(float* __restrict__ S, WaGeom g, const float* __restrict__ sink) {
@@ -667,12 +694,20 @@ extern "C" CC_API int cc_window_attention_sink(cc_device* dev, const cc_view* q,
     const int q_tiles = (int)((T + g.QT - 1) / g.QT);
     const int64_t band = window > 0 ? (int64_t)window - 1 + g.QT : last + 1;          // keys a query tile can see
     const int64_t band_max = band < last + 1 ? band : last + 1;
-    dim3 g1((unsigned)((band_max + WA_TILE - 1) / WA_TILE), (unsigned)q_tiles, (unsigned)G);
-    wa_scores_kernel<<<g1, WA_THREADS, 0, dev->stream>>>(qp, fptr(kring), (float*)Sp, g, scale, r1 ? fptr(r1) : nullptr, r2 ? fptr(r2) : nullptr);
+    const bool few_rows = T * H <= 64;
+    if (few_rows && (size_t)R * dk * 4 <= 160 * 1024) {
+        const size_t smem = (size_t)R * dk * 4;
+        if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(wa_scores_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) { cc_pool_free(dev, Sp, cls); return cc_fail(dev, CC_ERR_CUDA, "window_attention: %s", cudaGetErrorString(e)); } }
+        wa_scores_row_kernel<<<dim3((unsigned)((maxn + 7) / 8), (unsigned)T, (unsigned)G), 256, smem, dev->stream>>>(qp, fptr(kring), (float*)Sp, g, scale, r1 ? fptr(r1) : nullptr,
+                                                                                                                      r2 ? fptr(r2) : nullptr);
+    } else {
+        dim3 g1((unsigned)((band_max + WA_TILE - 1) / WA_TILE), (unsigned)q_tiles, (unsigned)G);
+        wa_scores_kernel<<<g1, WA_THREADS, 0, dev->stream>>>(qp, fptr(kring), (float*)Sp, g, scale, r1 ? fptr(r1) : nullptr, r2 ? fptr(r2) : nullptr);
+    }
     dev->launches++;
     wa_softmax_kernel<<<(unsigned)((T * H + 7) / 8), 256, 0, dev->stream>>>((float*)Sp, g, sink ? fptr(sink) : nullptr);
     dev->launches++;
-    if (T * H <= 64 && (size_t)maxn * 4 <= 160 * 1024) {
+    if (few_rows && (size_t)maxn * 4 <= 160 * 1024) {
         const size_t smem = (size_t)maxn * 4;
         if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(wa_values_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) { cc_pool_free(dev, Sp, cls); return cc_fail(dev, CC_ERR_CUDA, "window_attention: %s", cudaGetErrorString(e)); } }
         wa_values_row_kernel<<<dim3((unsigned)(T * H), (unsigned)((dv + 31) / 32)), 128, smem, dev->stream>>>((const float*)Sp, vptr, (float*)o->base, g);
@@ -790,101 +825,89 @@ extern "C" CC_API int cc_latent_ring_append(cc_device* dev, const cc_view* ring,
     return CC_OK;
 }
 
-// ---- per-head products that fold a latent cache's up-projections into the query and the output -----------------------------------------------------
+// ---- per-head products: the up-projections of a latent cache, folded into the query and applied to the attention result ---------------------
 #define HP_TOK 8
-// grid (ceil(T / 8), H): the CTA stages 8 tokens' q[t, h, :dim]; thread r owns latent coordinate r for those tokens and walks d upwards, so a
-// result's sum order does not depend on T or on the token's place in the call.  W: [H * dim, rank], read once per 8 tokens.
-__global__ void __launch_bounds__(128) head_absorb_kernel(const float* __restrict__ q, const float* __restrict__ W, float* __restrict__ out, int T, int H, int dim, int rest,
-                                                          int rank) {
-    extern __shared__ float ha_sm[];
+// grid (ceil(T / 8), H, ceil(n_out / 4)): the CTA stages 8 tokens' x[t, h, :n_in]; a warp owns one output coordinate for those tokens:
+// lane-strided partial sums over n_in, then the butterfly -- one order per output, whatever T is.  W: [H * n_out, n_in], rows read
+// contiguously.  The `rest` columns behind a head's n_in inputs are copied behind its n_out outputs.
+__global__ void __launch_bounds__(128) head_project_kernel(const float* __restrict__ x, const float* __restrict__ W, float* __restrict__ out, int T, int H, int n_in, int rest,
+                                                           int n_out) {
+    extern __shared__ float hp_sm[];
     const int t0 = blockIdx.x * HP_TOK, h = blockIdx.y;
-    const int qs = dim + rest, os = rank + rest;
-    for (int i = threadIdx.x; i < HP_TOK * dim; i += 128) {
-        const int tt = i / dim, d = i - tt * dim;
-        ha_sm[i] = t0 + tt < T ? q[((int64_t)(t0 + tt) * H + h) * qs + d] : 0.0f;
+    const int xs = n_in + rest, os = n_out + rest;
+    for (int i = threadIdx.x; i < HP_TOK * n_in; i += 128) {
+        const int tt = i / n_in, d = i - tt * n_in;
+        hp_sm[i] = t0 + tt < T ? x[((int64_t)(t0 + tt) * H + h) * xs + d] : 0.0f;
     }
-    __syncthreads();
-    for (int r = threadIdx.x; r < rank; r += 128) {
-        float acc[HP_TOK];
-#pragma unroll
-        for (int tt = 0; tt < HP_TOK; tt++) acc[tt] = 0.0f;
-        const float* wp = W + (int64_t)h * dim * rank + r;
-        for (int d = 0; d < dim; d++) {
-            const float wv = wp[(int64_t)d * rank];
-#pragma unroll
-            for (int tt = 0; tt < HP_TOK; tt++) acc[tt] = fmaf(ha_sm[tt * dim + d], wv, acc[tt]);
+    if (blockIdx.z == 0)
+        for (int i = threadIdx.x; i < HP_TOK * rest; i += 128) {
+            const int tt = i / rest, j = i - tt * rest;
+            if (t0 + tt < T) out[((int64_t)(t0 + tt) * H + h) * os + n_out + j] = x[((int64_t)(t0 + tt) * H + h) * xs + n_in + j];
         }
-#pragma unroll
-        for (int tt = 0; tt < HP_TOK; tt++)
-            if (t0 + tt < T) out[((int64_t)(t0 + tt) * H + h) * os + r] = acc[tt];
-    }
-    for (int i = threadIdx.x; i < HP_TOK * rest; i += 128) {
-        const int tt = i / rest, j = i - tt * rest;
-        if (t0 + tt < T) out[((int64_t)(t0 + tt) * H + h) * os + rank + j] = q[((int64_t)(t0 + tt) * H + h) * qs + dim + j];
-    }
-}
-extern "C" CC_API int cc_head_absorb(cc_device* dev, const cc_view* q, const cc_view* w, int32_t n_heads, int32_t dim, int32_t rest, cc_buf** out) {
-    SEQ_ENTER(dev, "head_absorb");
-    if (!out) return cc_fail(dev, CC_ERR_ARG, "head_absorb: out is NULL");
-    SEQ_F32(dev, q, "head_absorb q"); SEQ_F32(dev, w, "head_absorb w");
-    CC_REQUIRE(dev, q->ndim == 2 && w->ndim == 2 && n_heads > 0 && dim > 0 && rest >= 0 && q->shape[1] == (int64_t)n_heads * (dim + rest) && w->shape[0] == (int64_t)n_heads * dim,
-               "head_absorb: q must be [T, heads * (dim + rest)] and w [heads * dim, rank]");
-    const int64_t T = q->shape[0], rank = w->shape[1];
-    CC_REQUIRE(dev, (size_t)HP_TOK * dim * 4 <= 48 * 1024, "head_absorb: heads of %d do not fit shared memory", dim);
-    cc_buf* o = nullptr;
-    int rc = cc_new_activation(dev, T * n_heads * (rank + rest), CC_F32, false, &o);
-    if (rc) return rc;
-    *out = o;
-    if (T == 0) return CC_OK;
-    head_absorb_kernel<<<dim3((unsigned)((T + HP_TOK - 1) / HP_TOK), (unsigned)n_heads), 128, (size_t)HP_TOK * dim * 4, dev->stream>>>(fptr(q), fptr(w), (float*)o->base, (int)T,
-                                                                                                                                      n_heads, dim, rest, (int)rank);
-    CC_LAUNCH_CHECK(dev);
-    return CC_OK;
-}
-// grid (ceil(T / 8), H, ceil(vdim / 4)): the CTA stages 8 tokens' x[t, h, :rank]; a warp owns one output column: lane-strided partial sums over
-// the rank, then the butterfly (one order per output).  W: [H * vdim, rank].
-__global__ void __launch_bounds__(128) head_expand_kernel(const float* __restrict__ x, const float* __restrict__ W, float* __restrict__ out, int T, int H, int rank, int vdim) {
-    extern __shared__ float he_sm[];
-    const int t0 = blockIdx.x * HP_TOK, h = blockIdx.y;
-    for (int i = threadIdx.x; i < HP_TOK * rank; i += 128) {
-        const int tt = i / rank, r = i - tt * rank;
-        he_sm[i] = t0 + tt < T ? x[((int64_t)(t0 + tt) * H + h) * rank + r] : 0.0f;
-    }
     __syncthreads();
     const int v = blockIdx.z * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (v >= vdim) return;
-    const float* wp = W + ((int64_t)h * vdim + v) * rank;
+    if (v >= n_out) return;
+    const float* wp = W + ((int64_t)h * n_out + v) * n_in;
     float acc[HP_TOK];
 #pragma unroll
     for (int tt = 0; tt < HP_TOK; tt++) acc[tt] = 0.0f;
-    for (int r = lane; r < rank; r += 32) {
-        const float wv = wp[r];
+    for (int d = lane; d < n_in; d += 32) {
+        const float wv = wp[d];
 #pragma unroll
-        for (int tt = 0; tt < HP_TOK; tt++) acc[tt] = fmaf(he_sm[tt * rank + r], wv, acc[tt]);
+        for (int tt = 0; tt < HP_TOK; tt++) acc[tt] = fmaf(hp_sm[tt * n_in + d], wv, acc[tt]);
     }
 #pragma unroll
     for (int tt = 0; tt < HP_TOK; tt++) {
-        const float s = warp_sum(acc[tt]);
-        if (lane == 0 && t0 + tt < T) out[((int64_t)(t0 + tt) * H + h) * vdim + v] = s;
+        const float sum = warp_sum(acc[tt]);
+        if (lane == 0 && t0 + tt < T) out[((int64_t)(t0 + tt) * H + h) * os + v] = sum;
     }
 }
-extern "C" CC_API int cc_head_expand(cc_device* dev, const cc_view* x, const cc_view* w, int32_t n_heads, int32_t vdim, cc_buf** out) {
-    SEQ_ENTER(dev, "head_expand");
-    if (!out) return cc_fail(dev, CC_ERR_ARG, "head_expand: out is NULL");
-    SEQ_F32(dev, x, "head_expand x"); SEQ_F32(dev, w, "head_expand w");
-    CC_REQUIRE(dev, x->ndim == 2 && w->ndim == 2 && n_heads > 0 && vdim > 0 && w->shape[0] == (int64_t)n_heads * vdim && x->shape[1] == (int64_t)n_heads * w->shape[1],
-               "head_expand: x must be [T, heads * rank] and w [heads * vdim, rank]");
-    const int64_t T = x->shape[0], rank = w->shape[1];
-    const size_t smem = (size_t)HP_TOK * rank * 4;
-    CC_REQUIRE(dev, smem <= 160 * 1024, "head_expand: rank %lld does not fit shared memory", (long long)rank);
+extern "C" CC_API int cc_head_project(cc_device* dev, const cc_view* x, const cc_view* w, int32_t n_heads, int32_t rest, cc_buf** out) {
+    SEQ_ENTER(dev, "head_project");
+    if (!out) return cc_fail(dev, CC_ERR_ARG, "head_project: out is NULL");
+    SEQ_F32(dev, x, "head_project x"); SEQ_F32(dev, w, "head_project w");
+    CC_REQUIRE(dev, x->ndim == 2 && w->ndim == 2 && n_heads > 0 && rest >= 0 && w->shape[0] % n_heads == 0 && x->shape[1] == (int64_t)n_heads * (w->shape[1] + rest),
+               "head_project: x must be [T, heads * (n_in + rest)] and w [heads * n_out, n_in]");
+    const int64_t T = x->shape[0], n_in = w->shape[1], n_out = w->shape[0] / n_heads;
+    const size_t smem = (size_t)HP_TOK * n_in * 4;
+    CC_REQUIRE(dev, smem <= 160 * 1024, "head_project: %lld inputs per head do not fit shared memory", (long long)n_in);
     cc_buf* o = nullptr;
-    int rc = cc_new_activation(dev, T * n_heads * vdim, CC_F32, false, &o);
+    int rc = cc_new_activation(dev, T * n_heads * (n_out + rest), CC_F32, false, &o);
     if (rc) return rc;
     *out = o;
     if (T == 0) return CC_OK;
-    if (smem > 48 * 1024) CC_CUDA(dev, cudaFuncSetAttribute(head_expand_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    head_expand_kernel<<<dim3((unsigned)((T + HP_TOK - 1) / HP_TOK), (unsigned)n_heads, (unsigned)((vdim + 3) / 4)), 128, smem, dev->stream>>>(fptr(x), fptr(w), (float*)o->base,
-                                                                                                                                               (int)T, n_heads, (int)rank, vdim);
+    if (smem > 48 * 1024) CC_CUDA(dev, cudaFuncSetAttribute(head_project_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    head_project_kernel<<<dim3((unsigned)((T + HP_TOK - 1) / HP_TOK), (unsigned)n_heads, (unsigned)((n_out + 3) / 4)), 128, smem, dev->stream>>>(
+        fptr(x), fptr(w), (float*)o->base, (int)T, n_heads, (int)n_in, rest, (int)n_out);
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}
+
+// out[j, h] = [ a[j, h, :dim] | shared[j, col0 : col0 + rest] ]: every head's part followed by the columns all heads share.  One thread per element.
+__global__ void head_concat_shared_kernel(const float* __restrict__ a, const float* __restrict__ shared, float* __restrict__ out, int64_t n, int H, int dim, int rest, int scols,
+                                          int col0) {
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    const int hs = dim + rest;
+    const int c = (int)(idx % hs);
+    const int64_t jh = idx / hs, j = jh / H;
+    out[idx] = c < dim ? a[jh * dim + c] : shared[j * scols + col0 + (c - dim)];
+}
+extern "C" CC_API int cc_head_concat_shared(cc_device* dev, const cc_view* a, const cc_view* shared, int32_t n_heads, int32_t col0, int32_t rest, cc_buf** out) {
+    SEQ_ENTER(dev, "head_concat_shared");
+    if (!out) return cc_fail(dev, CC_ERR_ARG, "head_concat_shared: out is NULL");
+    SEQ_F32(dev, a, "head_concat_shared a"); SEQ_F32(dev, shared, "head_concat_shared shared");
+    CC_REQUIRE(dev, a->ndim == 2 && shared->ndim == 2 && n_heads > 0 && a->shape[1] % n_heads == 0 && shared->shape[0] >= a->shape[0] && col0 >= 0 && rest >= 0 &&
+                        col0 + rest <= shared->shape[1],
+               "head_concat_shared: a must be [rows, heads * dim], shared [>= rows, cols] with cols >= col0 + rest");
+    const int64_t rows = a->shape[0], dim = a->shape[1] / n_heads;
+    cc_buf* o = nullptr;
+    int rc = cc_new_activation(dev, rows * n_heads * (dim + rest), CC_F32, false, &o);
+    if (rc) return rc;
+    *out = o;
+    const int64_t n = rows * n_heads * (dim + rest);
+    if (n == 0) return CC_OK;
+    head_concat_shared_kernel<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>(fptr(a), fptr(shared), (float*)o->base, n, n_heads, (int)dim, rest, (int)shared->shape[1], col0);
     CC_LAUNCH_CHECK(dev);
     return CC_OK;
 }

@@ -161,8 +161,12 @@ class MeresunModel(SeqModel):
             lc.heads, lc.dim, lc.rot_dim, lc.vdim, lc.q_rank, lc.kv_rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["q_rank"], m["kv_rank"]
             lc.window, lc.scale, lc.rot_mag = (m["mask"]["size"] if m["mask"] else 0), m["scale"], 1.0
             t = {"norm1": up.vec(p + "norm1"), "dq": up.mat(p + "mix.dq"), "dq_norm": up.vec(p + "mix.dq.norm"), "uq": up.mat(p + "mix.uq"),
-                 "dkv": up.mat(p + "mix.dkv"), "dkv_norm": up.vec(p + "mix.dkv.norm"), "uk": up.mat32(p + "mix.uk"), "uv": up.mat32(p + "mix.uv"),
+                 "dkv": up.mat(p + "mix.dkv"), "dkv_norm": up.vec(p + "mix.dkv.norm"), "uk": up.mat(p + "mix.uk"), "uv": up.mat(p + "mix.uv"),
                  "o": up.mat(p + "mix.o")}
+            # the few-row pass folds the up-projections into the 32-bit scores and sums: F32 copies, the key one transposed head by head
+            uk = up.f32(p + "mix.uk").reshape(m["heads"], m["dim"], m["kv_rank"])
+            t["uk_t"] = up.table(np.ascontiguousarray(uk.transpose(0, 2, 1)).reshape(m["heads"] * m["kv_rank"], m["dim"]))
+            t["uv_f32"] = t["uv"] if dtype == "float32" else up.mat32(p + "mix.uv")
             if p + "mix.sink" in names:
                 t["sink"] = up.vec(p + "mix.sink")
             if m["rot"] and m["rot"]["dims"] > 0:

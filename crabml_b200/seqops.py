@@ -101,16 +101,16 @@ def latent_ring_append(ring, ckv, norm_w, eps, rank, freq, mag, pos0):
     ring.device.check(ring.device.lib.cc_latent_ring_append(ring.device.handle, _v(ring), _v(ckv), _v(norm_w), float(eps), int(rank), _v(freq), float(mag), int(pos0)))
 
 
-def head_absorb(q, w, n_heads, dim, rest):
+def head_project(x, w, n_heads, rest=0):
     h = C.c_void_p()
-    q.device.check(q.device.lib.cc_head_absorb(q.device.handle, _v(q), _v(w), int(n_heads), int(dim), int(rest), C.byref(h)))
-    return _new(q.device, h, [q.shape()[0], n_heads * (w.shape()[1] + rest)])
+    x.device.check(x.device.lib.cc_head_project(x.device.handle, _v(x), _v(w), int(n_heads), int(rest), C.byref(h)))
+    return _new(x.device, h, [x.shape()[0], n_heads * (w.shape()[0] // n_heads + rest)])
 
 
-def head_expand(x, w, n_heads, vdim):
+def head_concat_shared(a, shared, n_heads, col0, rest):
     h = C.c_void_p()
-    x.device.check(x.device.lib.cc_head_expand(x.device.handle, _v(x), _v(w), int(n_heads), int(vdim), C.byref(h)))
-    return _new(x.device, h, [x.shape()[0], n_heads * vdim])
+    a.device.check(a.device.lib.cc_head_concat_shared(a.device.handle, _v(a), _v(shared), int(n_heads), int(col0), int(rest), C.byref(h)))
+    return _new(a.device, h, [a.shape()[0], a.shape()[1] + n_heads * rest])
 
 
 def window_attention_sink(q, kring, vring, pos0, n_heads, n_kv, dk, dv, window, scale, sink=None, q_norm_w=None, eps=0.0, r1=None, r2=None):

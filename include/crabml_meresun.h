@@ -8,9 +8,11 @@
  *   g = gelu_tanh(W_sg x) * e_layer[token] ; y = W_sp g ; x += y / rms(y) * w_s.
  * Layers loop_start .. loop_stop-1 run loop_times times with the same weights; every run has its own cache, and before each run of
  * the block but the first the embedding output is added to x.
- * Mixer: latent attention.  Queries go through a normed latent; a cache row is [c | r] (cc_latent_ring_append); the per-head key and
- * value up-projections are folded into the query (cc_head_absorb) and applied to the attention result (cc_head_expand), so scores
- * and sums run over the cached rows themselves; sliding window, softmax with a per-head sink (cc_window_attention_sink).
+ * Mixer: latent attention.  Queries go through a normed latent; a cache row is [c | r] (cc_latent_ring_append); sliding window,
+ * softmax with a per-head sink (cc_window_attention_sink).  A pass of few rows (decoding) folds the per-head key up-projection into
+ * the query and applies the value up-projection to the attention result (cc_head_project), so scores and sums run over the cached
+ * rows themselves; a pass of many rows (prompts) expands the cached rows into per-head keys and values with two dense products and
+ * runs the same attention per head.
  * Feed-forward: dense with PolyNorm (cc_poly_norm), or routed (cc_moe_route_ex: sigmoid scores, group score = sum of the two
  * largest, renormalised weights; cc_moe_experts_glu: clamped gate and up, swish(1.702), up + 1), or none.
  */
@@ -49,13 +51,14 @@ typedef struct cmr_config {
     int32_t max_seq;                /* rows of the cache of a layer without a window.  <= 0: 4096 */
 } cmr_config;
 
-/* every pointer is a tensor uploaded by the caller; unused ones are NULL.  Matrices of dense products: F32 or BF16; uk, uv, router
- * and everything else: F32. */
+/* every pointer is a tensor uploaded by the caller; unused ones are NULL.  Matrices of dense products: F32 or BF16; uk_t, uv_f32,
+ * router and everything else: F32. */
 typedef struct cmr_layer_weights {
     cc_buf *norm1;                                  /* [width] */
     cc_buf *dq, *dq_norm, *uq;                      /* [q_rank, width], [q_rank], [heads * (dim + rot_dim), q_rank] */
     cc_buf *dkv, *dkv_norm;                         /* [kv_rank + rot_dim, width], [kv_rank] */
-    cc_buf *uk, *uv;                                /* [heads * dim, kv_rank], [heads * vdim, kv_rank] */
+    cc_buf *uk, *uv;                                /* [heads * dim, kv_rank], [heads * vdim, kv_rank]: dense products of the many-row pass */
+    cc_buf *uk_t, *uv_f32;                          /* few-row pass, F32: [heads * kv_rank, dim] (every head's block of uk transposed), uv itself */
     cc_buf *sink, *rot_freq, *o;                    /* [heads] or NULL, [P] frequencies of the rotated pairs (2 P <= rot_dim), [width, heads * vdim] */
     cc_buf *rg1, *rg1_b, *rg2, *rg2_b;              /* gates of the two results: [width, width], [width]; NULL = not gated */
     cc_buf *up, *down, *act;                        /* dense: [ff, width], [width, ff], [4] */

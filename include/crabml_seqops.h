@@ -101,13 +101,16 @@ CC_API int cc_rope_pairs(cc_device* dev, const cc_view* x, int32_t n_heads, int3
  * (freq [P], NULL = none), any further column is copied. */
 CC_API int cc_latent_ring_append(cc_device* dev, const cc_view* ring, const cc_view* ckv, const cc_view* norm_w, float eps, int32_t rank, const cc_view* freq,
                                  float mag, int64_t pos0);
-/* Folds a per-head key up-projection into the query, so that scores are taken against the latent rows themselves:
- *   out[t, h] = [ W_h^T q[t, h, :dim] | q[t, h, dim:] ]     q: [T, heads * (dim + rest)], w: [heads * dim, rank] (W_h = rows h*dim ..), F32
- * out: [T, heads * (rank + rest)].  (q_h . (W_h c) = (W_h^T q_h) . c) */
-CC_API int cc_head_absorb(cc_device* dev, const cc_view* q, const cc_view* w, int32_t n_heads, int32_t dim, int32_t rest, cc_buf** out);
-/* The per-head value up-projection of an attention result over latent rows: out[t, h] = W_h x[t, h]
- *   x: [T, heads * rank], w: [heads * vdim, rank] F32; out: [T, heads * vdim]. */
-CC_API int cc_head_expand(cc_device* dev, const cc_view* x, const cc_view* w, int32_t n_heads, int32_t vdim, cc_buf** out);
+/* A product per head, with the columns behind a head's inputs carried along:
+ *   out[t, h] = [ W_h x[t, h, :n_in] | x[t, h, n_in:] ]     x: [T, heads * (n_in + rest)], w: [heads * n_out, n_in] (W_h = rows h * n_out ..), F32
+ * out: [T, heads * (n_out + rest)].  With W_h the TRANSPOSED key up-projection of head h (n_out = rank) it folds that projection into the
+ * query, so that scores are taken against the latent rows themselves (q_h . (U_h c) = (U_h^T q_h) . c; the rotated part rides along as
+ * `rest`); with W_h the value up-projection and rest = 0 it turns an attention result over latent rows into the head's values. */
+CC_API int cc_head_project(cc_device* dev, const cc_view* x, const cc_view* w, int32_t n_heads, int32_t rest, cc_buf** out);
+
+/* out[j, h] = [ a[j, h] | shared[j, col0 : col0 + rest] ]: a: [rows, heads * dim]; shared: [>= rows, cols] (its first `rows` rows are used);
+ * out: [rows, heads * (dim + rest)].  Builds per-head keys out of their own part and a part all heads share (a latent cache's rotated columns). */
+CC_API int cc_head_concat_shared(cc_device* dev, const cc_view* a, const cc_view* shared, int32_t n_heads, int32_t col0, int32_t rest, cc_buf** out);
 
 /* ---- routed feed-forward ---------------------------------------------------------------------------------------------------- */
 /* x: [T, D]; router_w: [E, D] F32; correction: [E] or NULL.  s = softmax(router_w x) over all experts (32-bit).  Choice score =

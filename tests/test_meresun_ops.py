@@ -106,16 +106,21 @@ def test_latent_ring_append_norms_rotates_and_wraps(dev):
         seqops.latent_ring_append(ring, T32(dev, ckv[:8]), T32(dev, nw), 1e-5, rank, T32(dev, f), mag, 0)     # more rows than the ring holds
 
 
-@pytest.mark.parametrize("T,H,dim,rest,rank,vdim", [(1, 3, 8, 4, 20, 10), (9, 2, 12, 6, 14, 7), (70, 4, 4, 2, 11, 16), (17, 1, 32, 0, 64, 32), (8, 5, 3, 2, 130, 5)])
-def test_head_absorb_and_expand(dev, T, H, dim, rest, rank, vdim):
+@pytest.mark.parametrize("T,H,n_in,rest,n_out", [(1, 3, 8, 4, 20), (9, 2, 12, 6, 14), (70, 4, 4, 2, 11), (17, 1, 32, 0, 64), (8, 5, 130, 2, 3), (3, 2, 600, 64, 5)])
+def test_head_project(dev, T, H, n_in, rest, n_out):
     rng = np.random.default_rng(T * 10 + H)
-    q = rng.standard_normal((T, H, dim + rest)); uk = rng.standard_normal((H * dim, rank)) / 3
-    got = seqops.head_absorb(T32(dev, q.reshape(T, -1)), T32(dev, uk), H, dim, rest).export().reshape(T, H, rank + rest)
-    want = np.concatenate([np.einsum("thd,hdr->thr", q[..., :dim], uk.reshape(H, dim, rank)), q[..., dim:]], -1)
-    assert np.abs(got - want).max() < 1e-5
-    x = rng.standard_normal((T, H, rank)); uv = rng.standard_normal((H * vdim, rank)) / 3
-    got = seqops.head_expand(T32(dev, x.reshape(T, -1)), T32(dev, uv), H, vdim).export().reshape(T, H, vdim)
-    assert np.abs(got - np.einsum("thr,hvr->thv", x, uv.reshape(H, vdim, rank))).max() < 2e-5
+    x = rng.standard_normal((T, H, n_in + rest)); w = rng.standard_normal((H * n_out, n_in)) / 3
+    got = seqops.head_project(T32(dev, x.reshape(T, -1)), T32(dev, w), H, rest).export().reshape(T, H, n_out + rest)
+    want = np.concatenate([np.einsum("thd,hnd->thn", x[..., :n_in], w.reshape(H, n_out, n_in)), x[..., n_in:]], -1)
+    assert np.abs(got - want).max() < 3e-5
+
+
+def test_head_concat_shared(dev):
+    rng = np.random.default_rng(8)
+    a = rng.standard_normal((11, 3, 5)); shared = rng.standard_normal((14, 9))
+    got = seqops.head_concat_shared(T32(dev, a.reshape(11, -1)), T32(dev, shared), 3, 4, 3).export().reshape(11, 3, 8)
+    want = np.concatenate([a, np.repeat(shared[:11, None, 4:7], 3, 1)], -1)
+    assert np.array_equal(got, want.astype(np.float32))
 
 
 # ---- the whole mixer out of the ops, against the reference's one function ----------------------------------------------------------------
@@ -129,10 +134,12 @@ def mixer_weights(rng, D, H, dn, dr, dv, qr, kr, sink_scale=1.0):
 class Mixer:
     """the op chain of one latent-attention layer on one sequence, fed in portions (what the runner's mixer does)"""
 
-    def __init__(self, dev, w, m, ring_rows, eps=1e-5):
+    def __init__(self, dev, w, m, ring_rows, eps=1e-5, expand_over=64):
         from crabml_b200 import CudaTensor
-        self.dev, self.m, self.eps, self.at = dev, m, eps, 0
+        self.dev, self.m, self.eps, self.at, self.expand_over, self.rows = dev, m, eps, 0, expand_over, ring_rows
         self.w = {k: T32(dev, v) for k, v in w.items()}
+        uk = np.asarray(w["m.uk"], np.float32).reshape(m["heads"], m["dim"], m["kv_rank"])
+        self.w["m.uk_t"] = T32(dev, np.ascontiguousarray(uk.transpose(0, 2, 1)).reshape(-1, m["dim"]))
         f, self.mag = rotary.table_of(m["rot"])
         self.f = T32(dev, f)
         self.ring = CudaTensor.alloc([ring_rows, m["kv_rank"] + m["rot_dim"]], capi.F32, dev)
@@ -144,9 +151,17 @@ class Mixer:
         seqops.latent_ring_append(self.ring, w["m.dkv"].matmul_vec(hd), w["m.dkv.norm"], self.eps, kr, self.f, self.mag, self.at)
         cq = seqops.group_rms_norm(w["m.dq"].matmul_vec(hd), w["m.dq.norm"], 1, self.eps)
         q = seqops.rope_pairs(w["m.uq"].matmul_vec(cq), H, dn + dr, dn, self.f, self.mag, self.at)
-        ql = seqops.head_absorb(q, w["m.uk"], H, dn, dr)
-        ol = seqops.window_attention_sink(ql, self.ring, None, self.at, H, 1, kr + dr, kr, m["mask"]["size"], m["scale"], sink=w.get("m.sink"))
-        out = w["m.o"].matmul_vec(seqops.head_expand(ol, w["m.uv"], H, dv)).export().reshape(n, -1)
+        if n * H > self.expand_over:              # many rows: per-head keys and values of the ring's rows, then attention per head
+            from crabml_b200 import TensorStrider
+            rows = min(self.rows, self.at + n)
+            lat = self.ring.with_strider(TensorStrider([rows, kr], [kr + dr, 1])).contiguous()
+            keys = seqops.head_concat_shared(w["m.uk"].matmul_vec(lat), self.ring, H, kr, dr)
+            o = seqops.window_attention_sink(q, keys, w["m.uv"].matmul_vec(lat), self.at, H, H, dn + dr, dv, m["mask"]["size"], m["scale"], sink=w.get("m.sink"))
+        else:                                     # few rows: the up-projections folded into the query and applied to the result
+            ql = seqops.head_project(q, w["m.uk_t"], H, dr)
+            ol = seqops.window_attention_sink(ql, self.ring, None, self.at, H, 1, kr + dr, kr, m["mask"]["size"], m["scale"], sink=w.get("m.sink"))
+            o = seqops.head_project(ol, w["m.uv"], H, 0)
+        out = w["m.o"].matmul_vec(o).export().reshape(n, -1)
         self.at += n
         return out
 
@@ -159,13 +174,14 @@ def test_latent_attention_whole_and_in_portions(dev, H, dn, dr, dv, qr, kr, wind
     w = mixer_weights(rng, D, H, dn, dr, dv, qr, kr)
     h = rng.standard_normal((T, D))
     want = R.latent_attention(h.astype(np.float32).astype(np.float64), w, "m.", m, 1e-5)
-    for portions in ([T], [1] * T, [29] + [1] * 32, [2, 3, 30, 2, 17, 1, 1, 5], [2] * 30 + [1]):
-        mx = Mixer(dev, w, m, window - 1 + max(portions))                 # the smallest ring that holds the window behind the longest portion
-        got = np.concatenate([mx.feed(h[a:a + n]) for a, n in zip(np.cumsum([0] + portions[:-1]), portions)])
-        assert np.abs(got - want).max() < 3e-5 * max(1.0, np.abs(want).max()), portions
+    for expand_over in (64, 0, 10 ** 9):              # the runner's rule, every pass expanded, every pass folded
+        for portions in ([T], [1] * T, [29] + [1] * 32, [2, 3, 30, 2, 17, 1, 1, 5], [2] * 30 + [1]):
+            mx = Mixer(dev, w, m, window - 1 + max(portions), expand_over=expand_over)      # the smallest ring that holds the window behind the longest portion
+            got = np.concatenate([mx.feed(h[a:a + n]) for a, n in zip(np.cumsum([0] + portions[:-1]), portions)])
+            assert np.abs(got - want).max() < 3e-5 * max(1.0, np.abs(want).max()), (expand_over, portions)
 
 
-def _crafted(dev, window, T, j_star, sink=-1e30, ring_rows=None, portions=None):
+def _crafted(dev, window, T, j_star, sink=-1e30, ring_rows=None, portions=None, expand_over=8):
     """One head; every query and the key at j_star point the same way in the rotation-free part, strongly, so that whoever sees
     j_star returns (nearly) its value and nobody else does.  -> output [T, dv] with value coordinate 0 = 1 only at j_star."""
     H, dn, dr, dv, qr, kr, D = 1, 4, 2, 3, 4, 4, 8
@@ -179,7 +195,7 @@ def _crafted(dev, window, T, j_star, sink=-1e30, ring_rows=None, portions=None):
     h = np.zeros((T, D)); h[:, 0] = 1.0       # c = normed (1, 0, 0, 0) = (2, 0, 0, 0): k_plain = 0, v = (0, 2, 0)
     h[j_star, :2] = (0.0, 1.0)                # at j_star c = (0, 2, 0, 0): k_plain[0] = 2 -> score 30 * 2 * 2 = 120 for every query with c_q[0] = 2
     portions = portions or [T]
-    mx = Mixer(dev, w, m, ring_rows or window - 1 + max(portions))
+    mx = Mixer(dev, w, m, ring_rows or window - 1 + max(portions), expand_over=expand_over)
     got = np.concatenate([mx.feed(h[a:a + n]) for a, n in zip(np.cumsum([0] + portions[:-1]), portions)])
     want = R.latent_attention(h, w, "m.", m, 1e-5)
     assert np.abs(got - want).max() < 1e-4
