@@ -465,18 +465,30 @@ __global__ void __launch_bounds__(WA_THREADS) wa_scores_kernel(const float* __re
     for (int a = 0; a < 4; a++)
 #pragma unroll
         for (int b = 0; b < 4; b++) acc[a][b] = 0.0f;
-    for (int d0 = 0; d0 < g.dk; d0 += WA_K) {
+    // the next 16 coordinates of queries and keys are fetched into registers while the current ones are multiplied
+    float pq[4], pk[4];
+    auto fetch = [&](int d0) {
 #pragma unroll
         for (int e = 0; e < 4; e++) {
             const int idx = threadIdx.x + e * WA_THREADS;
             const int r = idx >> 4, dd = idx & 15;
             const int tq = r / g.R, hr = r - tq * g.R;
             const bool din = d0 + dd < g.dk;
-            sq[dd][r] = (din && tq < tq_n) ? q[((int64_t)(t0 + tq) * g.H + kvh * g.R + hr) * g.dk + d0 + dd] : 0.0f;
+            pq[e] = (din && tq < tq_n) ? q[((int64_t)(t0 + tq) * g.H + kvh * g.R + hr) * g.dk + d0 + dd] : 0.0f;
             const int64_t j = j0 + r;
-            sk[dd][r] = (din && j <= i_last) ? kring[(j % g.ring) * g.krs + kvh * g.dk + d0 + dd] : 0.0f;
+            pk[e] = (din && j <= i_last) ? kring[(j % g.ring) * g.krs + kvh * g.dk + d0 + dd] : 0.0f;
+        }
+    };
+    fetch(0);
+    for (int d0 = 0; d0 < g.dk; d0 += WA_K) {
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int idx = threadIdx.x + e * WA_THREADS;
+            sq[idx & 15][idx >> 4] = pq[e];
+            sk[idx & 15][idx >> 4] = pk[e];
         }
         __syncthreads();
+        if (d0 + WA_K < g.dk) fetch(d0 + WA_K);
 #pragma unroll
         for (int dd = 0; dd < WA_K; dd++) {
             const float4 qv = *(const float4*)&sq[dd][ty * 4];
@@ -602,7 +614,10 @@ __global__ void __launch_bounds__(WA_THREADS) wa_values_kernel(const float* __re
     for (int a = 0; a < 4; a++)
 #pragma unroll
         for (int b = 0; b < 4; b++) acc[a][b] = 0.0f;
-    for (int64_t j0 = band_lo; j0 <= i_last; j0 += WA_K) {
+    // the next block of 16 keys (probabilities and values) is fetched into registers while the current one is multiplied: the loads' latency
+    // hides behind the arithmetic of a CTA that often has its SM to itself
+    float pp[4], pv[4];
+    auto fetch = [&](int64_t j0) {
 #pragma unroll
         for (int e = 0; e < 4; e++) {
             const int idx = threadIdx.x + e * WA_THREADS;
@@ -614,20 +629,30 @@ __global__ void __launch_bounds__(WA_THREADS) wa_values_kernel(const float* __re
                     const int64_t i = i_first + tq, lo = wa_lo(g, i), j = j0 + kk;
                     if (j >= lo && j <= i) p = S[((int64_t)(t0 + tq) * g.H + kvh * g.R + hr) * g.cap + (j - lo)];
                 }
-                sp[kk][r] = p;
+                pp[e] = p;
             }
             {   // values: consecutive threads read consecutive columns of one key
                 const int kk = idx >> 6, c = idx & 63;
                 const int64_t j = j0 + kk;
-                sv[kk][c] = (j <= i_last && c0 + c < g.dv) ? vring[(j % g.ring) * g.vrs + kvh * g.vhs + c0 + c] : 0.0f;
+                pv[e] = (j <= i_last && c0 + c < g.dv) ? vring[(j % g.ring) * g.vrs + kvh * g.vhs + c0 + c] : 0.0f;
             }
         }
+    };
+    fetch(band_lo);
+    for (int64_t j0 = band_lo; j0 <= i_last; j0 += WA_K) {
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int idx = threadIdx.x + e * WA_THREADS;
+            sp[idx & 15][idx >> 4] = pp[e];
+            sv[idx >> 6][idx & 63] = pv[e];
+        }
         __syncthreads();
+        if (j0 + WA_K <= i_last) fetch(j0 + WA_K);
 #pragma unroll
         for (int kk = 0; kk < WA_K; kk++) {
-            const float4 pv = *(const float4*)&sp[kk][ty * 4];
+            const float4 pv4 = *(const float4*)&sp[kk][ty * 4];
             const float4 vv = *(const float4*)&sv[kk][tx * 4];
-            const float pr[4] = {pv.x, pv.y, pv.z, pv.w}, vr[4] = {vv.x, vv.y, vv.z, vv.w};
+            const float pr[4] = {pv4.x, pv4.y, pv4.z, pv4.w}, vr[4] = {vv.x, vv.y, vv.z, vv.w};
 #pragma unroll
             for (int a = 0; a < 4; a++)
 #pragma unroll
