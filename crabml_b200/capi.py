@@ -213,7 +213,7 @@ def load_library(build_if_missing: bool = True):
         "cc_window_attention_sink": (i32, [vp, pv, pv, f32, pv, pv, i64, i32, i32, i32, i32, i32, f32, pv, pv, pv, pp]),
         "cc_rope_pairs": (i32, [vp, pv, i32, i32, i32, pv, f32, i64]),
         "cc_latent_ring_append": (i32, [vp, pv, pv, pv, f32, i32, pv, f32, i64]),
-        "cc_head_project": (i32, [vp, pv, pv, i32, i32, pp]),
+        "cc_head_project": (i32, [vp, pv, pv, i32, i32, pv, f32, i64, pp]),
         "cc_head_concat_shared": (i32, [vp, pv, pv, i32, i32, i32, pp]),
         "cc_moe_route_ex": (i32, [vp, pv, pv, pv, C.POINTER(cc_route_params), pp, pp]),
         "cc_moe_experts_glu": (i32, [vp, pv, pv, pv, pv, pv, pv, i32, i32, C.POINTER(cc_glu_params), pp]),

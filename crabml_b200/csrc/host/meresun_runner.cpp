@@ -81,11 +81,11 @@ struct Runner : csr_runner {
         cq = norm(cq, L.dq_norm, 1);
         CudaTensor q = L.uq.matmul_vec(cq);
         cc_view qv = q.view();
-        if (freq) check(cc_rope_pairs(dev, &qv, c.heads, c.dim + c.rot_dim, c.dim, freq, c.rot_mag, pos0));
         cc_buf* b = nullptr;
         cc_view rv = ring.view(), sk{};
         CudaTensor o;
         if (n * c.heads > 64) {
+            if (freq) check(cc_rope_pairs(dev, &qv, c.heads, c.dim + c.rot_dim, c.dim, freq, c.rot_mag, pos0));
             // many rows: expand the cached rows once for all queries of the pass.  The expansion keeps the ring's row order (position p in
             // row p % ring), so the attention reads it like the ring itself; rows no token has written yet are never visible.
             const int64_t rows = std::min<int64_t>(L.ring, pos0 + n);
@@ -101,9 +101,10 @@ struct Runner : csr_runner {
                                            opt(L.sink, sk), &b));
             o = adopt(b, {n, (int64_t)c.heads * c.vdim});
         } else {
-            // few rows: all heads read the one cached row per position; keys are whole rows, values their first kv_rank columns
+            // few rows: all heads read the one cached row per position; keys are whole rows, values their first kv_rank columns.  The
+            // query's rotated part is turned while it is carried past the fold.
             cc_view ukv = L.uk_t.view();
-            check(cc_head_project(dev, &qv, &ukv, c.heads, c.rot_dim, &b));
+            check(cc_head_project(dev, &qv, &ukv, c.heads, c.rot_dim, freq, c.rot_mag, pos0, &b));
             CudaTensor ql = adopt(b, {n, (int64_t)c.heads * (c.kv_rank + c.rot_dim)});
             cc_view qlv = ql.view();
             b = nullptr;
@@ -112,7 +113,7 @@ struct Runner : csr_runner {
             CudaTensor ol = adopt(b, {n, (int64_t)c.heads * c.kv_rank});
             cc_view olv = ol.view(), uvv = L.uv_f32.view();
             b = nullptr;
-            check(cc_head_project(dev, &olv, &uvv, c.heads, 0, &b));
+            check(cc_head_project(dev, &olv, &uvv, c.heads, 0, nullptr, 1.0f, 0, &b));
             o = adopt(b, {n, (int64_t)c.heads * c.vdim});
         }
         return L.o.matmul_vec(o);
@@ -180,6 +181,9 @@ struct Runner : csr_runner {
     }
 
     CudaTensor logits_of(const CudaTensor& x, const std::vector<int64_t>& rows) override {
+        bool all = (int64_t)rows.size() == x.shape()[0];
+        for (size_t i = 0; all && i < rows.size(); i++) all = rows[i] == (int64_t)i;
+        if (all) return head.matmul_vec(norm(x, final_norm, conf.norm_groups));          // every row in order (a decoded token): no copy
         CudaTensor xs = CudaTensor::alloc({(int64_t)rows.size(), conf.width}, CC_F32, dev);
         xs.copy_rows_from(x, rows);
         return head.matmul_vec(norm(xs, final_norm, conf.norm_groups));
@@ -212,8 +216,6 @@ extern "C" CC_API int cmr_runner_create(cc_device* dev, const cmr_config* conf, 
             const cmr_layer_weights& w = lw[i];
             const std::string at = "layer " + std::to_string(i) + ": ";
             if (c.heads < 1 || c.dim < 1 || c.rot_dim < 0 || c.vdim < 1 || c.q_rank < 1 || c.kv_rank < 1) throw TensorError(at + "bad head counts / sizes");
-            if (c.heads > 64) throw TensorError(at + "more than 64 heads over one shared cache row are not supported");
-            if (c.vdim > 0 && c.kv_rank + c.rot_dim < c.kv_rank) throw TensorError(at + "bad sizes");
             auto need = [&](cc_buf* b, const char* name, std::vector<int64_t> shape) {
                 if (!b) throw TensorError(at + "tensor '" + name + "' is missing");
                 return CudaTensor::wrap(dev, b, shape);

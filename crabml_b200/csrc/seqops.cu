@@ -570,16 +570,33 @@ __global__ void wa_softmax_kernel(float* __restrict__ S, WaGeom g, const float* 
 // few rows (decoding): grid (rows, ceil(dv / 32)); a CTA owns 32 output columns of one row = (query, head).  The row's probabilities go to
 // shared memory; the visible keys are cut into four contiguous quarters, warp w adds quarter w in ascending order for its lane's column,
 // and the quarters are added as (p0 + p1) + (p2 + p3).  The order depends on the row alone (its number of visible keys), not on T.
-__global__ void __launch_bounds__(128) wa_values_row_kernel(const float* __restrict__ S, const float* __restrict__ vring, float* __restrict__ out, WaGeom g) {
+// S holds the raw scores: every CTA of a row redoes the row's softmax in shared memory (warp 0, the sums in wa_softmax_kernel's order, so the
+// weights are the same bits), which saves a launch per layer in decoding.
+__global__ void __launch_bounds__(128) wa_values_row_kernel(const float* __restrict__ S, const float* __restrict__ vring, float* __restrict__ out, WaGeom g,
+                                                            const float* __restrict__ sink) {
     extern __shared__ float wr_sm[];
     __shared__ float part[4][32];
     const int64_t row = blockIdx.x;
     const int t = (int)(row / g.H), h = (int)(row % g.H), kvh = h / g.R;
     const int64_t i = g.pos0 + t, lo = wa_lo(g, i);
     const int n = (int)(i - lo + 1);
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     for (int c = threadIdx.x; c < n; c += 128) wr_sm[c] = S[row * g.cap + c];
     __syncthreads();
-    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    if (w == 0) {
+        float mx = -INFINITY;
+        for (int c = lane; c < n; c += 32) mx = fmaxf(mx, wr_sm[c]);
+        mx = warp_max(mx);
+        const float sk = sink ? sink[h] : -INFINITY;
+        mx = fmaxf(mx, sk);
+        float sum = 0.0f;
+        for (int c = lane; c < n; c += 32) { const float e = expf(wr_sm[c] - mx); wr_sm[c] = e; sum += e; }
+        sum = warp_sum(sum);
+        if (sink) sum += expf(sk - mx);
+        const float inv = 1.0f / sum;
+        for (int c = lane; c < n; c += 32) wr_sm[c] *= inv;
+    }
+    __syncthreads();
     const int d = blockIdx.y * 32 + lane;
     const int per = (n + 3) >> 2;
     const int c_begin = min(n, w * per), c_end = min(n, c_begin + per);
@@ -730,12 +747,15 @@ extern "C" CC_API int cc_window_attention_sink(cc_device* dev, const cc_view* q,
         wa_scores_kernel<<<g1, WA_THREADS, 0, dev->stream>>>(qp, fptr(kring), (float*)Sp, g, scale, r1 ? fptr(r1) : nullptr, r2 ? fptr(r2) : nullptr);
     }
     dev->launches++;
-    wa_softmax_kernel<<<(unsigned)((T * H + 7) / 8), 256, 0, dev->stream>>>((float*)Sp, g, sink ? fptr(sink) : nullptr);
-    dev->launches++;
-    if (few_rows && (size_t)maxn * 4 <= 160 * 1024) {
+    const bool row_values = few_rows && (size_t)maxn * 4 <= 160 * 1024;
+    if (!row_values) {
+        wa_softmax_kernel<<<(unsigned)((T * H + 7) / 8), 256, 0, dev->stream>>>((float*)Sp, g, sink ? fptr(sink) : nullptr);
+        dev->launches++;
+    }
+    if (row_values) {
         const size_t smem = (size_t)maxn * 4;
         if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(wa_values_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) { cc_pool_free(dev, Sp, cls); return cc_fail(dev, CC_ERR_CUDA, "window_attention: %s", cudaGetErrorString(e)); } }
-        wa_values_row_kernel<<<dim3((unsigned)(T * H), (unsigned)((dv + 31) / 32)), 128, smem, dev->stream>>>((const float*)Sp, vptr, (float*)o->base, g);
+        wa_values_row_kernel<<<dim3((unsigned)(T * H), (unsigned)((dv + 31) / 32)), 128, smem, dev->stream>>>((const float*)Sp, vptr, (float*)o->base, g, sink ? fptr(sink) : nullptr);
     } else {
         dim3 g3((unsigned)((dv + WA_TILE - 1) / WA_TILE), (unsigned)q_tiles, (unsigned)G);
         wa_values_kernel<<<g3, WA_THREADS, 0, dev->stream>>>((const float*)Sp, vptr, (float*)o->base, g);
@@ -856,7 +876,7 @@ extern "C" CC_API int cc_latent_ring_append(cc_device* dev, const cc_view* ring,
 // lane-strided partial sums over n_in, then the butterfly -- one order per output, whatever T is.  W: [H * n_out, n_in], rows read
 // contiguously.  The `rest` columns behind a head's n_in inputs are copied behind its n_out outputs.
 __global__ void __launch_bounds__(128) head_project_kernel(const float* __restrict__ x, const float* __restrict__ W, float* __restrict__ out, int T, int H, int n_in, int rest,
-                                                           int n_out) {
+                                                           int n_out, const float* __restrict__ freq, int half, float mag, int64_t pos0) {
     extern __shared__ float hp_sm[];
     const int t0 = blockIdx.x * HP_TOK, h = blockIdx.y;
     const int xs = n_in + rest, os = n_out + rest;
@@ -864,11 +884,21 @@ __global__ void __launch_bounds__(128) head_project_kernel(const float* __restri
         const int tt = i / n_in, d = i - tt * n_in;
         hp_sm[i] = t0 + tt < T ? x[((int64_t)(t0 + tt) * H + h) * xs + d] : 0.0f;
     }
-    if (blockIdx.z == 0)
-        for (int i = threadIdx.x; i < HP_TOK * rest; i += 128) {
-            const int tt = i / rest, j = i - tt * rest;
+    if (blockIdx.z == 0) {
+        // the carried columns: the first 2 * half of them are rotated on the way when a frequency table is given
+        for (int i = threadIdx.x; i < HP_TOK * half; i += 128) {
+            const int tt = i / half, p = i - tt * half;
+            if (t0 + tt >= T) continue;
+            const float* src = x + ((int64_t)(t0 + tt) * H + h) * xs + n_in + 2 * p;
+            float* dst = out + ((int64_t)(t0 + tt) * H + h) * os + n_out + 2 * p;
+            rotate_pair(src[0], src[1], (float)(pos0 + t0 + tt), freq[p], mag, dst[0], dst[1]);
+        }
+        const int plain = rest - 2 * half;
+        for (int i = threadIdx.x; i < HP_TOK * plain; i += 128) {
+            const int tt = i / plain, j = 2 * half + (i - tt * plain);
             if (t0 + tt < T) out[((int64_t)(t0 + tt) * H + h) * os + n_out + j] = x[((int64_t)(t0 + tt) * H + h) * xs + n_in + j];
         }
+    }
     __syncthreads();
     const int v = blockIdx.z * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (v >= n_out) return;
@@ -887,8 +917,10 @@ __global__ void __launch_bounds__(128) head_project_kernel(const float* __restri
         if (lane == 0 && t0 + tt < T) out[((int64_t)(t0 + tt) * H + h) * os + v] = sum;
     }
 }
-extern "C" CC_API int cc_head_project(cc_device* dev, const cc_view* x, const cc_view* w, int32_t n_heads, int32_t rest, cc_buf** out) {
+extern "C" CC_API int cc_head_project(cc_device* dev, const cc_view* x, const cc_view* w, int32_t n_heads, int32_t rest, const cc_view* freq, float mag, int64_t pos0,
+                                      cc_buf** out) {
     SEQ_ENTER(dev, "head_project");
+    if (freq) { SEQ_F32(dev, freq, "head_project freq"); CC_REQUIRE(dev, 2 * view_len(freq) <= rest && pos0 >= 0, "head_project: more rotated pairs than carried columns"); }
     if (!out) return cc_fail(dev, CC_ERR_ARG, "head_project: out is NULL");
     SEQ_F32(dev, x, "head_project x"); SEQ_F32(dev, w, "head_project w");
     CC_REQUIRE(dev, x->ndim == 2 && w->ndim == 2 && n_heads > 0 && rest >= 0 && w->shape[0] % n_heads == 0 && x->shape[1] == (int64_t)n_heads * (w->shape[1] + rest),
@@ -903,7 +935,7 @@ extern "C" CC_API int cc_head_project(cc_device* dev, const cc_view* x, const cc
     if (T == 0) return CC_OK;
     if (smem > 48 * 1024) CC_CUDA(dev, cudaFuncSetAttribute(head_project_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     head_project_kernel<<<dim3((unsigned)((T + HP_TOK - 1) / HP_TOK), (unsigned)n_heads, (unsigned)((n_out + 3) / 4)), 128, smem, dev->stream>>>(
-        fptr(x), fptr(w), (float*)o->base, (int)T, n_heads, (int)n_in, rest, (int)n_out);
+        fptr(x), fptr(w), (float*)o->base, (int)T, n_heads, (int)n_in, rest, (int)n_out, freq ? fptr(freq) : nullptr, freq ? (int)view_len(freq) : 0, mag, pos0);
     CC_LAUNCH_CHECK(dev);
     return CC_OK;
 }

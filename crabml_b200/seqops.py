@@ -101,9 +101,10 @@ def latent_ring_append(ring, ckv, norm_w, eps, rank, freq, mag, pos0):
     ring.device.check(ring.device.lib.cc_latent_ring_append(ring.device.handle, _v(ring), _v(ckv), _v(norm_w), float(eps), int(rank), _v(freq), float(mag), int(pos0)))
 
 
-def head_project(x, w, n_heads, rest=0):
+def head_project(x, w, n_heads, rest=0, freq=None, mag=1.0, pos0=0):
+    """freq: the first 2 * len(freq) carried columns are rotated on the way (rows are positions pos0 ..)"""
     h = C.c_void_p()
-    x.device.check(x.device.lib.cc_head_project(x.device.handle, _v(x), _v(w), int(n_heads), int(rest), C.byref(h)))
+    x.device.check(x.device.lib.cc_head_project(x.device.handle, _v(x), _v(w), int(n_heads), int(rest), _v(freq), float(mag), int(pos0), C.byref(h)))
     return _new(x.device, h, [x.shape()[0], n_heads * (w.shape()[0] // n_heads + rest)])
 
 

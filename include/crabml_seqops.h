@@ -105,8 +105,11 @@ CC_API int cc_latent_ring_append(cc_device* dev, const cc_view* ring, const cc_v
  *   out[t, h] = [ W_h x[t, h, :n_in] | x[t, h, n_in:] ]     x: [T, heads * (n_in + rest)], w: [heads * n_out, n_in] (W_h = rows h * n_out ..), F32
  * out: [T, heads * (n_out + rest)].  With W_h the TRANSPOSED key up-projection of head h (n_out = rank) it folds that projection into the
  * query, so that scores are taken against the latent rows themselves (q_h . (U_h c) = (U_h^T q_h) . c; the rotated part rides along as
- * `rest`); with W_h the value up-projection and rest = 0 it turns an attention result over latent rows into the head's values. */
-CC_API int cc_head_project(cc_device* dev, const cc_view* x, const cc_view* w, int32_t n_heads, int32_t rest, cc_buf** out);
+ * `rest`); with W_h the value up-projection and rest = 0 it turns an attention result over latent rows into the head's values.
+ * freq ([P], 2 P <= rest, or NULL): the first 2 P carried columns are rotated on the way like cc_rope_pairs does (rows are positions
+ * pos0 ..), which saves the separate rotation of a query that is folded anyway. */
+CC_API int cc_head_project(cc_device* dev, const cc_view* x, const cc_view* w, int32_t n_heads, int32_t rest, const cc_view* freq, float mag, int64_t pos0,
+                           cc_buf** out);
 
 /* out[j, h] = [ a[j, h] | shared[j, col0 : col0 + rest] ]: a: [rows, heads * dim]; shared: [>= rows, cols] (its first `rows` rows are used);
  * out: [rows, heads * (dim + rest)].  Builds per-head keys out of their own part and a part all heads share (a latent cache's rotated columns). */

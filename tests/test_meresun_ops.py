@@ -115,6 +115,18 @@ def test_head_project(dev, T, H, n_in, rest, n_out):
     assert np.abs(got - want).max() < 3e-5
 
 
+def test_head_project_rotates_carried_columns(dev):
+    rng = np.random.default_rng(9)
+    T, H, n_in, rest, n_out, pos0 = 11, 3, 6, 7, 5, 123
+    r = rot(4)
+    f, mag = rotary.table_of(r)
+    x = rng.standard_normal((T, H, n_in + rest)); w = rng.standard_normal((H * n_out, n_in))
+    got = seqops.head_project(T32(dev, x.reshape(T, -1)), T32(dev, w), H, rest, T32(dev, f), mag, pos0).export().reshape(T, H, n_out + rest)
+    want = np.concatenate([np.einsum("thd,hnd->thn", x[..., :n_in], w.reshape(H, n_out, n_in)),
+                           R.rotate_pairs(x[..., n_in:n_in + 4], pos0 + np.arange(T), *R.rotary_frequencies(r)), x[..., n_in + 4:]], -1)
+    assert np.abs(got - want).max() < 3e-5
+
+
 def test_head_concat_shared(dev):
     rng = np.random.default_rng(8)
     a = rng.standard_normal((11, 3, 5)); shared = rng.standard_normal((14, 9))
@@ -150,15 +162,16 @@ class Mixer:
         hd = T32(self.dev, h)
         seqops.latent_ring_append(self.ring, w["m.dkv"].matmul_vec(hd), w["m.dkv.norm"], self.eps, kr, self.f, self.mag, self.at)
         cq = seqops.group_rms_norm(w["m.dq"].matmul_vec(hd), w["m.dq.norm"], 1, self.eps)
-        q = seqops.rope_pairs(w["m.uq"].matmul_vec(cq), H, dn + dr, dn, self.f, self.mag, self.at)
+        q = w["m.uq"].matmul_vec(cq)
         if n * H > self.expand_over:              # many rows: per-head keys and values of the ring's rows, then attention per head
             from crabml_b200 import TensorStrider
+            q = seqops.rope_pairs(q, H, dn + dr, dn, self.f, self.mag, self.at)
             rows = min(self.rows, self.at + n)
             lat = self.ring.with_strider(TensorStrider([rows, kr], [kr + dr, 1])).contiguous()
             keys = seqops.head_concat_shared(w["m.uk"].matmul_vec(lat), self.ring, H, kr, dr)
             o = seqops.window_attention_sink(q, keys, w["m.uv"].matmul_vec(lat), self.at, H, H, dn + dr, dv, m["mask"]["size"], m["scale"], sink=w.get("m.sink"))
         else:                                     # few rows: the up-projections folded into the query and applied to the result
-            ql = seqops.head_project(q, w["m.uk_t"], H, dr)
+            ql = seqops.head_project(q, w["m.uk_t"], H, dr, self.f, self.mag, self.at)     # the rotated part is turned on the way
             ol = seqops.window_attention_sink(ql, self.ring, None, self.at, H, 1, kr + dr, kr, m["mask"]["size"], m["scale"], sink=w.get("m.sink"))
             o = seqops.head_project(ol, w["m.uv"], H, 0)
         out = w["m.o"].matmul_vec(o).export().reshape(n, -1)
