@@ -90,7 +90,7 @@ class cmr_config(C.Structure):
                [(n, C.c_int32) for n in ("norm_groups", "loop_start", "loop_stop", "loop_times", "side_dim", "chunk", "max_seq")]
 
 
-CMR_WEIGHT_FIELDS = ("norm1", "dq", "dq_norm", "uq", "dkv", "dkv_norm", "uk", "uv", "uk_t", "uv_f32", "sink", "rot_freq", "o", "rg1", "rg1_b", "rg2", "rg2_b", "up", "down", "act",
+CMR_WEIGHT_FIELDS = ("norm1", "h_stack", "dq_norm", "uq", "dkv_norm", "uk", "uv", "uk_t", "uv_f32", "sink", "rot_freq", "o", "rg1_b", "rg2_b", "down", "act",
                      "router", "correction", "e_gate", "e_up", "e_down", "side_table", "side_gate", "side_proj", "side_norm")
 
 
@@ -213,6 +213,7 @@ def load_library(build_if_missing: bool = True):
         "cc_window_attention_sink": (i32, [vp, pv, pv, f32, pv, pv, i64, i32, i32, i32, i32, i32, f32, pv, pv, pv, pp]),
         "cc_rope_pairs": (i32, [vp, pv, i32, i32, i32, pv, f32, i64]),
         "cc_latent_ring_append": (i32, [vp, pv, pv, pv, f32, i32, pv, f32, i64]),
+        "cc_split_cols": (i32, [vp, pv, i32, C.POINTER(i32), pp]),
         "cc_head_project": (i32, [vp, pv, pv, i32, i32, pv, f32, i64, pp]),
         "cc_head_concat_shared": (i32, [vp, pv, pv, i32, i32, i32, pp]),
         "cc_moe_route_ex": (i32, [vp, pv, pv, pv, C.POINTER(cc_route_params), pp, pp]),

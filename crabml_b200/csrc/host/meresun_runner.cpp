@@ -3,6 +3,7 @@
 // in which order the tensor ops run.  Slots, step and greedy generation are the shared ones of seq_runner.hpp.
 //
 //   run:     h = group_norm(x) ; x += mixer(h) * sigmoid(W_g1 h + b1) + ff(h) * sigmoid(W_g2 h + b2) ; x += token_side(x, token)
+//            (W_dkv, W_dq, W_g1, W_g2 and a dense W_up all multiply h: they are one stacked matrix and one product, cut afterwards)
 //   mixer:   c_q = norm(W_dq h) ; q = W_uq c_q, rotated part turned ; row [norm(c) | turned r] of W_dkv h into the run's ring ; then
 //            few rows (decoding): q folded through W_uk ; windowed softmax with a sink over the ring's rows ; result through W_uv per head
 //            many rows (prompts): keys [W_uk c | r] and values W_uv c of the ring's rows as dense products ; the same attention per head
@@ -22,8 +23,10 @@ namespace {
 
 struct Layer {
     cmr_layer_config c{};
-    CudaTensor norm1, dq, dq_norm, uq, dkv, dkv_norm, uk, uv, uk_t, uv_f32, sink, rot_freq, o, rg1, rg1_b, rg2, rg2_b, up, down, act, router, correction, e_gate, e_up, e_down, side_table,
+    CudaTensor norm1, h_stack, dq_norm, uq, dkv_norm, uk, uv, uk_t, uv_f32, sink, rot_freq, o, rg1_b, rg2_b, down, act, router, correction, e_gate, e_up, e_down, side_table,
         side_gate, side_proj, side_norm;
+    std::vector<int32_t> widths;                         // column blocks of h_stack's product, in order
+    int i_g1 = -1, i_g2 = -1, i_up = -1;                 // which block is which (blocks 0 and 1: the cache row, the query latent); -1: absent
     int64_t ring = 0;            // rows of the latent cache of one run of this layer
 };
 // a run of a layer: looped layers run several times with the same weights, each time on a cache of its own
@@ -64,20 +67,19 @@ struct Runner : csr_runner {
         return h;
     }
 
-    CudaTensor mixer(const Layer& L, CudaTensor& ring, const CudaTensor& h, int64_t pos0) {
+    // ckv: the new tokens' raw cache rows W_dkv h; cq: their raw query latents W_dq h
+    CudaTensor mixer(const Layer& L, CudaTensor& ring, const CudaTensor& ckv, CudaTensor cq, int64_t pos0) {
         const auto& c = L.c;
-        const int64_t n = h.shape()[0];
+        const int64_t n = ckv.shape()[0];
         if (c.window <= 0 && pos0 + n > L.ring) throw TensorError("a sequence of " + std::to_string(pos0 + n) + " tokens does not fit the cache of " + std::to_string(L.ring));
         cc_view fq{};
         const cc_view* freq = opt(L.rot_freq, fq);
         // the cache row of every new token
         {
-            CudaTensor ckv = L.dkv.matmul_vec(h);
             cc_view rv = ring.view(), cv = ckv.view(), nw{};
             check(cc_latent_ring_append(dev, &rv, &cv, opt(L.dkv_norm, nw), conf.norm_eps, c.kv_rank, freq, c.rot_mag, pos0));
         }
         // queries through their latent
-        CudaTensor cq = L.dq.matmul_vec(h);
         cq = norm(cq, L.dq_norm, 1);
         CudaTensor q = L.uq.matmul_vec(cq);
         cc_view qv = q.view();
@@ -119,11 +121,11 @@ struct Runner : csr_runner {
         return L.o.matmul_vec(o);
     }
 
-    CudaTensor feed_forward(const Layer& L, const CudaTensor& h) {
+    // z: the dense feed-forward's W_up h (unused by a routed one)
+    CudaTensor feed_forward(const Layer& L, const CudaTensor& h, CudaTensor z) {
         const auto& c = L.c;
         const int64_t n = h.shape()[0];
         if (c.ff_kind == CMR_FF_DENSE) {
-            CudaTensor z = L.up.matmul_vec(h);
             cc_view zv = z.view(), av = L.act.view();
             check(cc_poly_norm(dev, &zv, &av, conf.norm_eps));
             return L.down.matmul_vec(z);
@@ -156,12 +158,20 @@ struct Runner : csr_runner {
             if (runs[ri].add_embedding) x = std::move(x).add_inplace(x0);
             {
                 CudaTensor h = norm(x, L.norm1, conf.norm_groups);
-                CudaTensor y = mixer(L, s.ring[ri], h, pos0);
+                std::vector<CudaTensor> part;
+                {
+                    CudaTensor all = L.h_stack.matmul_vec(h);
+                    cc_view av = all.view();
+                    std::vector<cc_buf*> outs(L.widths.size(), nullptr);
+                    check(cc_split_cols(dev, &av, (int32_t)L.widths.size(), L.widths.data(), outs.data()));
+                    for (size_t p = 0; p < outs.size(); p++) part.push_back(adopt(outs[p], {n, L.widths[p]}));
+                }
+                CudaTensor y = mixer(L, s.ring[ri], part[0], part[1], pos0);
                 CudaTensor g1, f, g2;
-                if (L.rg1.valid()) g1 = L.rg1.matmul_vec(h);
+                if (L.i_g1 >= 0) g1 = part[L.i_g1];
                 if (L.c.ff_kind != CMR_FF_NONE) {
-                    f = feed_forward(L, h);
-                    if (L.rg2.valid()) g2 = L.rg2.matmul_vec(h);
+                    f = feed_forward(L, h, L.i_up >= 0 ? part[L.i_up] : CudaTensor());
+                    if (L.i_g2 >= 0) g2 = part[L.i_g2];
                 }
                 cc_view xv = x.view(), yv = y.view(), g1v{}, b1v{}, fv{}, g2v{}, b2v{};
                 check(cc_gated_sum(dev, &xv, 1, &yv, opt(g1, g1v), opt(L.rg1_b, b1v), opt(f, fv), opt(g2, g2v), opt(L.rg2_b, b2v)));
@@ -223,8 +233,17 @@ extern "C" CC_API int cmr_runner_create(cc_device* dev, const cmr_config* conf, 
             auto maybe = [&](cc_buf* b, std::vector<int64_t> shape) { return b ? CudaTensor::wrap(dev, b, shape) : CudaTensor(); };
             const int64_t qh = c.dim + c.rot_dim, hv = (int64_t)c.heads * c.vdim;
             L.norm1 = need(w.norm1, "norm1", {D});
-            L.dq = need(w.dq, "mix.dq", {c.q_rank, D}); L.dq_norm = need(w.dq_norm, "mix.dq.norm", {c.q_rank}); L.uq = need(w.uq, "mix.uq", {c.heads * qh, c.q_rank});
-            L.dkv = need(w.dkv, "mix.dkv", {(int64_t)c.kv_rank + c.rot_dim, D}); L.dkv_norm = need(w.dkv_norm, "mix.dkv.norm", {c.kv_rank});
+            L.dq_norm = need(w.dq_norm, "mix.dq.norm", {c.q_rank}); L.uq = need(w.uq, "mix.uq", {c.heads * qh, c.q_rank});
+            L.dkv_norm = need(w.dkv_norm, "mix.dkv.norm", {c.kv_rank});
+            L.rg1_b = maybe(w.rg1_b, {D}); L.rg2_b = maybe(w.rg2_b, {D});
+            if (c.ff_kind == CMR_FF_NONE && L.rg2_b.valid()) throw TensorError(at + "a gate for a feed-forward the layer does not have");
+            L.widths = {c.kv_rank + c.rot_dim, c.q_rank};
+            if (L.rg1_b.valid()) { L.i_g1 = (int)L.widths.size(); L.widths.push_back((int32_t)D); }
+            if (L.rg2_b.valid()) { L.i_g2 = (int)L.widths.size(); L.widths.push_back((int32_t)D); }
+            if (c.ff_kind == CMR_FF_DENSE) { if (c.ff < 1) throw TensorError(at + "bad feed-forward width"); L.i_up = (int)L.widths.size(); L.widths.push_back(c.ff); }
+            int64_t on_h = 0;
+            for (int32_t v : L.widths) on_h += v;
+            L.h_stack = need(w.h_stack, "the stack of mix.dkv, mix.dq, rg1, rg2, mlp.up", {on_h, D});
             L.uk = need(w.uk, "mix.uk", {(int64_t)c.heads * c.dim, c.kv_rank}); L.uv = need(w.uv, "mix.uv", {hv, c.kv_rank});
             L.uk_t = need(w.uk_t, "mix.uk (per head transposed)", {(int64_t)c.heads * c.kv_rank, c.dim}); L.uv_f32 = need(w.uv_f32, "mix.uv (F32)", {hv, c.kv_rank});
             L.o = need(w.o, "mix.o", {D, hv});
@@ -235,11 +254,8 @@ extern "C" CC_API int cmr_runner_create(cc_device* dev, const cmr_config* conf, 
                 L.rot_freq = CudaTensor::wrap(dev, w.rot_freq, {pairs});
             }
             if (L.uk_t.dtype() != CC_F32 || L.uv_f32.dtype() != CC_F32) throw TensorError(at + "the folded forms of mix.uk / mix.uv must be F32: they enter the 32-bit scores and sums");
-            L.rg1 = maybe(w.rg1, {D, D}); L.rg1_b = maybe(w.rg1_b, {D}); L.rg2 = maybe(w.rg2, {D, D}); L.rg2_b = maybe(w.rg2_b, {D});
-            if ((L.rg1_b.valid() && !L.rg1.valid()) || (L.rg2_b.valid() && !L.rg2.valid())) throw TensorError(at + "a gate's bias without the gate");
             if (c.ff_kind == CMR_FF_DENSE) {
-                if (c.ff < 1) throw TensorError(at + "bad feed-forward width");
-                L.up = need(w.up, "mlp.up", {c.ff, D}); L.down = need(w.down, "mlp.down", {D, c.ff}); L.act = need(w.act, "mlp.act", {4});
+                L.down = need(w.down, "mlp.down", {D, c.ff}); L.act = need(w.act, "mlp.act", {4});
             } else if (c.ff_kind == CMR_FF_ROUTED) {
                 if (c.experts < 1 || c.top < 1 || c.top > c.experts || c.ff < 1) throw TensorError(at + "bad router sizes");
                 L.router = need(w.router, "mlp.router", {c.experts, D});

@@ -969,6 +969,50 @@ extern "C" CC_API int cc_head_concat_shared(cc_device* dev, const cc_view* a, co
     return CC_OK;
 }
 
+// ---- column blocks of one product's result as separate tensors ------------------------------------------------------------------------------
+#define SPLIT_MAX 8
+struct SplitArgs {
+    float* dst[SPLIT_MAX];
+    int end[SPLIT_MAX];          // first column behind part p
+    int n;
+};
+__global__ void split_cols_kernel(const float* __restrict__ src, SplitArgs a, int64_t total, int cols) {
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int64_t r = idx / cols;
+    const int c = (int)(idx - r * cols);
+    int p = 0;
+    while (p + 1 < a.n && c >= a.end[p]) p++;
+    const int begin = p ? a.end[p - 1] : 0;
+    a.dst[p][r * (a.end[p] - begin) + (c - begin)] = src[idx];
+}
+extern "C" CC_API int cc_split_cols(cc_device* dev, const cc_view* src, int32_t n_parts, const int32_t* widths, cc_buf** outs) {
+    SEQ_ENTER(dev, "split_cols");
+    if (!widths || !outs) return cc_fail(dev, CC_ERR_ARG, "split_cols: widths / outs is NULL");
+    SEQ_F32(dev, src, "split_cols src");
+    CC_REQUIRE(dev, src->ndim == 2 && n_parts >= 1 && n_parts <= SPLIT_MAX, "split_cols: src must be [rows, cols], 1..%d parts", SPLIT_MAX);
+    const int64_t rows = src->shape[0], cols = src->shape[1];
+    int64_t sum = 0;
+    for (int p = 0; p < n_parts; p++) { CC_REQUIRE(dev, widths[p] >= 1, "split_cols: empty part %d", p); sum += widths[p]; }
+    CC_REQUIRE(dev, sum == cols, "split_cols: the parts have %lld columns, src %lld", (long long)sum, (long long)cols);
+    SplitArgs a;
+    a.n = n_parts;
+    int end = 0;
+    for (int p = 0; p < n_parts; p++) {
+        cc_buf* o = nullptr;
+        int rc = cc_new_activation(dev, rows * widths[p], CC_F32, false, &o);
+        if (rc) { for (int q = 0; q < p; q++) { cc_tensor_release(outs[q]); outs[q] = nullptr; } return rc; }
+        outs[p] = o;
+        a.dst[p] = (float*)o->base;
+        a.end[p] = (end += widths[p]);
+    }
+    const int64_t total = rows * cols;
+    if (total == 0) return CC_OK;
+    split_cols_kernel<<<(unsigned)((total + 255) / 256), 256, 0, dev->stream>>>(fptr(src), a, total, (int)cols);
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}
+
 // ---- PolyNorm ------------------------------------------------------------------------------------------------------------------------------
 // one CTA per row: thread-strided sums of z^2, z^4, z^6, a fixed tree over the 256 partial sums, then the weighted sum of the three unit powers
 __global__ void __launch_bounds__(256) poly_norm_kernel(float* __restrict__ z, const float* __restrict__ coef, int cols, float eps) {

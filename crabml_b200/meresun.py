@@ -160,9 +160,10 @@ class MeresunModel(SeqModel):
             lc = lcs[i]
             lc.heads, lc.dim, lc.rot_dim, lc.vdim, lc.q_rank, lc.kv_rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["q_rank"], m["kv_rank"]
             lc.window, lc.scale, lc.rot_mag = (m["mask"]["size"] if m["mask"] else 0), m["scale"], 1.0
-            t = {"norm1": up.vec(p + "norm1"), "dq": up.mat(p + "mix.dq"), "dq_norm": up.vec(p + "mix.dq.norm"), "uq": up.mat(p + "mix.uq"),
-                 "dkv": up.mat(p + "mix.dkv"), "dkv_norm": up.vec(p + "mix.dkv.norm"), "uk": up.mat(p + "mix.uk"), "uv": up.mat(p + "mix.uv"),
-                 "o": up.mat(p + "mix.o")}
+            t = {"norm1": up.vec(p + "norm1"), "dq_norm": up.vec(p + "mix.dq.norm"), "uq": up.mat(p + "mix.uq"), "dkv_norm": up.vec(p + "mix.dkv.norm"),
+                 "uk": up.mat(p + "mix.uk"), "uv": up.mat(p + "mix.uv"), "o": up.mat(p + "mix.o")}
+            # one product for everything that multiplies the layer's normed input (the order include/crabml_meresun.h gives)
+            on_h = [p + "mix.dkv", p + "mix.dq"]
             # the few-row pass folds the up-projections into the 32-bit scores and sums: F32 copies, the key one transposed head by head
             uk = up.f32(p + "mix.uk").reshape(m["heads"], m["dim"], m["kv_rank"])
             t["uk_t"] = up.table(np.ascontiguousarray(uk.transpose(0, 2, 1)).reshape(m["heads"] * m["kv_rank"], m["dim"]))
@@ -174,11 +175,15 @@ class MeresunModel(SeqModel):
                 t["rot_freq"], lc.rot_mag = up.table(freq), mag
             for g in ("rg1", "rg2"):
                 if p + g in names and (g == "rg1" or mlp):
-                    t[g], t[g + "_b"] = up.mat(p + g), up.vec(p + g + ".b")
+                    on_h.append(p + g)
+                    t[g + "_b"] = up.vec(p + g + ".b")
+            if mlp and mlp["kind"] == "dense":
+                on_h.append(p + "mlp.up")
+            t["h_stack"] = up.stack(on_h)
             lc.ff_kind = FF_KINDS[mlp["kind"]] if mlp else 0
             if mlp and mlp["kind"] == "dense":
                 lc.ff = mlp["ff"]
-                t["up"], t["down"], t["act"] = up.mat(p + "mlp.up"), up.mat(p + "mlp.down"), up.vec(p + "mlp.act")
+                t["down"], t["act"] = up.mat(p + "mlp.down"), up.vec(p + "mlp.act")
             elif mlp:
                 r = mlp["router"]
                 lc.ff, lc.limit = mlp["expert"]["ff"], mlp["expert"]["limit"]

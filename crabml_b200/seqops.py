@@ -76,6 +76,14 @@ def moe_experts(x, ids, weights, w_gate, w_up, w_down, n_experts, ff, act=capi.A
     return _new(x.device, h, list(x.shape()))
 
 
+def split_cols(src, widths):
+    n = len(widths)
+    w = (C.c_int32 * n)(*[int(v) for v in widths])
+    outs = (C.c_void_p * n)()
+    src.device.check(src.device.lib.cc_split_cols(src.device.handle, _v(src), n, w, outs))
+    return [_new(src.device, C.c_void_p(outs[i]), [src.shape()[0], int(widths[i])]) for i in range(n)]
+
+
 def group_rms_norm(x, w, groups, eps, dst=None):
     dst = dst if dst is not None else type(x).alloc(x.shape(), capi.F32, x.device)
     x.device.check(x.device.lib.cc_group_rms_norm(x.device.handle, _v(dst), _v(x), _v(w), int(groups), float(eps)))

@@ -55,13 +55,17 @@ typedef struct cmr_config {
  * router and everything else: F32. */
 typedef struct cmr_layer_weights {
     cc_buf *norm1;                                  /* [width] */
-    cc_buf *dq, *dq_norm, *uq;                      /* [q_rank, width], [q_rank], [heads * (dim + rot_dim), q_rank] */
-    cc_buf *dkv, *dkv_norm;                         /* [kv_rank + rot_dim, width], [kv_rank] */
+    /* everything that multiplies the layer's normed input h, stacked one under the other so that it is ONE product: mix.dkv
+     * [kv_rank + rot_dim, width], mix.dq [q_rank, width], then rg1 [width, width] if rg1_b is given, rg2 [width, width] if rg2_b is
+     * given, mlp.up [ff, width] if the feed-forward is dense */
+    cc_buf *h_stack;
+    cc_buf *dq_norm, *uq;                           /* [q_rank], [heads * (dim + rot_dim), q_rank] */
+    cc_buf *dkv_norm;                               /* [kv_rank] */
     cc_buf *uk, *uv;                                /* [heads * dim, kv_rank], [heads * vdim, kv_rank]: dense products of the many-row pass */
     cc_buf *uk_t, *uv_f32;                          /* few-row pass, F32: [heads * kv_rank, dim] (every head's block of uk transposed), uv itself */
     cc_buf *sink, *rot_freq, *o;                    /* [heads] or NULL, [P] frequencies of the rotated pairs (2 P <= rot_dim), [width, heads * vdim] */
-    cc_buf *rg1, *rg1_b, *rg2, *rg2_b;              /* gates of the two results: [width, width], [width]; NULL = not gated */
-    cc_buf *up, *down, *act;                        /* dense: [ff, width], [width, ff], [4] */
+    cc_buf *rg1_b, *rg2_b;                          /* biases of the gates of the two results: [width]; NULL = that result is not gated */
+    cc_buf *down, *act;                             /* dense: [width, ff], [4] */
     cc_buf *router, *correction;                    /* routed: [experts, width], [experts] */
     cc_buf *e_gate, *e_up, *e_down;                 /* routed: expert-major stacks [experts * ff, width] x 2, [experts * width, ff] */
     cc_buf *side_table, *side_gate, *side_proj, *side_norm;   /* [vocab, side_dim] (this layer's part), [side_dim, width], [width, side_dim], [width] */

@@ -44,6 +44,10 @@ CC_API int cc_poly_norm(cc_device* dev, const cc_view* z, const cc_view* coef, f
  * that operand is not gated; y2 NULL: one operand.  The residual update of a block whose sublayers run side by side on one input. */
 CC_API int cc_gated_sum(cc_device* dev, const cc_view* dst, int32_t accumulate, const cc_view* y1, const cc_view* g1, const cc_view* b1, const cc_view* y2,
                         const cc_view* g2, const cc_view* b2);
+/* src [rows, cols] cut into n_parts (<= 8) blocks of neighbouring columns, widths[p] wide, each returned as a contiguous tensor
+ * [rows, widths[p]] in outs[p].  For matrices that multiply the same input and are stacked one under the other: ONE product (one launch,
+ * one conversion of the input), then this. */
+CC_API int cc_split_cols(cc_device* dev, const cc_view* src, int32_t n_parts, const int32_t* widths, cc_buf** outs);
 /* gate = act(gate) * up, elementwise (the inner step of a gated feed-forward, exact 32-bit activation) */
 CC_API int cc_glu_inplace(cc_device* dev, const cc_view* gate, const cc_view* up, int32_t act);
 

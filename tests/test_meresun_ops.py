@@ -47,6 +47,19 @@ def test_group_rms_norm(dev, rows, cols, groups):
     assert np.abs(got - R.group_rms_norm(x, w, groups, 1e-5)).max() < 1e-5
 
 
+def test_split_cols(dev):
+    rng = np.random.default_rng(4)
+    x = rng.standard_normal((13, 30)).astype(np.float32)
+    for widths in ([30], [1, 29], [7, 3, 11, 9], [4, 4, 4, 4, 4, 4, 3, 3]):
+        parts = seqops.split_cols(T32(dev, x), widths)
+        at = 0
+        for p, wd in zip(parts, widths):
+            assert np.array_equal(p.export().reshape(13, wd), x[:, at:at + wd])
+            at += wd
+    with pytest.raises(capi.TensorError):
+        seqops.split_cols(T32(dev, x), [10, 10])
+
+
 @pytest.mark.parametrize("cols", [1, 7, 320, 1000])
 def test_poly_norm(dev, cols):
     rng = np.random.default_rng(cols)
