@@ -617,6 +617,74 @@ __global__ void __launch_bounds__(128) wa_values_row_kernel(const float* __restr
     __syncthreads();
     if (w == 0 && d < g.dv) out[row * g.dv + d] = (part[0][lane] + part[1][lane]) + (part[2][lane] + part[3][lane]);
 }
+// few rows, R > 1 query heads per key/value head: grid (T * G, ceil(dv / 32)), 512 threads.  A CTA owns 32 value columns of ALL R heads of
+// one (token, key/value head), so every value row is read once for the group instead of once per head.  Each head's softmax is redone
+// in shared memory by one warp (wa_softmax_kernel's order); the visible keys are cut into 16 contiguous segments, warp w adds segment w in
+// ascending order into R accumulators per lane, and the segments are added in ascending order.  The order depends on the row alone.
+template <int R>
+__global__ void __launch_bounds__(512) wa_values_group_kernel(const float* __restrict__ S, const float* __restrict__ vring, float* __restrict__ out, WaGeom g,
+                                                              const float* __restrict__ sink) {
+    extern __shared__ float wg_sm[];
+    const int t = blockIdx.x / g.G, kvh = blockIdx.x % g.G;
+    const int64_t i = g.pos0 + t, lo = wa_lo(g, i);
+    const int n = (int)(i - lo + 1);
+    float* pr = wg_sm;                            // [R][n]
+    float* part = wg_sm + (size_t)R * n;          // [16][R][32]
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    for (int hr = w; hr < R; hr += 16) {
+        const int h = kvh * R + hr;
+        const float* Sr = S + ((int64_t)t * g.H + h) * g.cap;
+        float* p = pr + (size_t)hr * n;
+        float mx = -INFINITY;
+        for (int c = lane; c < n; c += 32) { const float v = Sr[c]; p[c] = v; mx = fmaxf(mx, v); }
+        mx = warp_max(mx);
+        const float sk = sink ? sink[h] : -INFINITY;
+        mx = fmaxf(mx, sk);
+        float sum = 0.0f;
+        for (int c = lane; c < n; c += 32) { const float e = expf(p[c] - mx); p[c] = e; sum += e; }
+        sum = warp_sum(sum);
+        if (sink) sum += expf(sk - mx);
+        const float inv = 1.0f / sum;
+        for (int c = lane; c < n; c += 32) p[c] *= inv;
+    }
+    __syncthreads();
+    const int d = blockIdx.y * 32 + lane;
+    const int per = (n + 15) >> 4;
+    const int c_begin = min(n, w * per), c_end = min(n, c_begin + per);
+    float acc[R];
+#pragma unroll
+    for (int hr = 0; hr < R; hr++) acc[hr] = 0.0f;
+    if (d < g.dv) {
+        const float* vb = vring + (int64_t)kvh * g.vhs + d;
+        const int64_t rs = g.vrs;
+        int r = (int)(lo % g.ring) + c_begin;
+        if (r >= g.ring) r -= g.ring;
+#pragma unroll 4
+        for (int c = c_begin; c < c_end; c++) {
+            const float v = vb[r * rs];
+#pragma unroll
+            for (int hr = 0; hr < R; hr++) acc[hr] = fmaf(pr[(size_t)hr * n + c], v, acc[hr]);
+            if (++r == g.ring) r = 0;
+        }
+    }
+#pragma unroll
+    for (int hr = 0; hr < R; hr++) part[(w * R + hr) * 32 + lane] = acc[hr];
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < R * 32; idx += 512) {
+        const int hr = idx >> 5, l = idx & 31;
+        float sum = 0.0f;
+#pragma unroll
+        for (int ww = 0; ww < 16; ww++) sum += part[(ww * R + hr) * 32 + l];
+        const int col = blockIdx.y * 32 + l;
+        if (col < g.dv) out[((int64_t)t * g.H + kvh * R + hr) * g.dv + col] = sum;
+    }
+}
+template <int R>
+static cudaError_t wa_launch_group(cc_device* dev, const float* S, const float* v, float* out, const WaGeom& g, const float* sink, size_t smem) {
+    if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(wa_values_group_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; }
+    wa_values_group_kernel<R><<<dim3((unsigned)(g.T * g.G), (unsigned)((g.dv + 31) / 32)), 512, smem, dev->stream>>>(S, v, out, g, sink);
+    return cudaSuccess;
+}
 // grid (dv tiles, query tiles, G)
 __global__ void __launch_bounds__(WA_THREADS) wa_values_kernel(const float* __restrict__ S, const float* __restrict__ vring, float* __restrict__ out, WaGeom g) {
     __shared__ float sp[WA_K][WA_TILE + 4];       // [key][row]
@@ -747,12 +815,21 @@ extern "C" CC_API int cc_window_attention_sink(cc_device* dev, const cc_view* q,
         wa_scores_kernel<<<g1, WA_THREADS, 0, dev->stream>>>(qp, fptr(kring), (float*)Sp, g, scale, r1 ? fptr(r1) : nullptr, r2 ? fptr(r2) : nullptr);
     }
     dev->launches++;
-    const bool row_values = few_rows && (size_t)maxn * 4 <= 160 * 1024;
+    const size_t group_smem = ((size_t)R * maxn + 16 * (size_t)R * 32) * 4;
+    const bool group_values = few_rows && (R == 2 || R == 4 || R == 8 || R == 16) && group_smem <= 160 * 1024;
+    const bool row_values = group_values || (few_rows && (size_t)maxn * 4 <= 160 * 1024);
     if (!row_values) {
         wa_softmax_kernel<<<(unsigned)((T * H + 7) / 8), 256, 0, dev->stream>>>((float*)Sp, g, sink ? fptr(sink) : nullptr);
         dev->launches++;
     }
-    if (row_values) {
+    if (group_values) {
+        const float* sp = sink ? fptr(sink) : nullptr;
+        cudaError_t e = R == 2 ? wa_launch_group<2>(dev, (const float*)Sp, vptr, (float*)o->base, g, sp, group_smem)
+                      : R == 4 ? wa_launch_group<4>(dev, (const float*)Sp, vptr, (float*)o->base, g, sp, group_smem)
+                      : R == 8 ? wa_launch_group<8>(dev, (const float*)Sp, vptr, (float*)o->base, g, sp, group_smem)
+                               : wa_launch_group<16>(dev, (const float*)Sp, vptr, (float*)o->base, g, sp, group_smem);
+        if (e != cudaSuccess) { cc_pool_free(dev, Sp, cls); return cc_fail(dev, CC_ERR_CUDA, "window_attention: %s", cudaGetErrorString(e)); }
+    } else if (row_values) {
         const size_t smem = (size_t)maxn * 4;
         if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(wa_values_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) { cc_pool_free(dev, Sp, cls); return cc_fail(dev, CC_ERR_CUDA, "window_attention: %s", cudaGetErrorString(e)); } }
         wa_values_row_kernel<<<dim3((unsigned)(T * H), (unsigned)((dv + 31) / 32)), 128, smem, dev->stream>>>((const float*)Sp, vptr, (float*)o->base, g, sink ? fptr(sink) : nullptr);
@@ -976,15 +1053,15 @@ struct SplitArgs {
     int end[SPLIT_MAX];          // first column behind part p
     int n;
 };
-__global__ void split_cols_kernel(const float* __restrict__ src, SplitArgs a, int64_t total, int cols) {
-    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= total) return;
-    const int64_t r = idx / cols;
-    const int c = (int)(idx - r * cols);
+// grid (ceil(cols / 256), min(rows, 65535)): a thread owns one column (its part is found once) and walks the rows of its grid line
+__global__ void split_cols_kernel(const float* __restrict__ src, SplitArgs a, int64_t rows, int cols) {
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c >= cols) return;
     int p = 0;
     while (p + 1 < a.n && c >= a.end[p]) p++;
-    const int begin = p ? a.end[p - 1] : 0;
-    a.dst[p][r * (a.end[p] - begin) + (c - begin)] = src[idx];
+    const int begin = p ? a.end[p - 1] : 0, w = a.end[p] - begin;
+    float* dst = a.dst[p] + (c - begin);
+    for (int64_t r = blockIdx.y; r < rows; r += gridDim.y) dst[r * w] = src[r * cols + c];
 }
 extern "C" CC_API int cc_split_cols(cc_device* dev, const cc_view* src, int32_t n_parts, const int32_t* widths, cc_buf** outs) {
     SEQ_ENTER(dev, "split_cols");
@@ -1008,7 +1085,7 @@ extern "C" CC_API int cc_split_cols(cc_device* dev, const cc_view* src, int32_t 
     }
     const int64_t total = rows * cols;
     if (total == 0) return CC_OK;
-    split_cols_kernel<<<(unsigned)((total + 255) / 256), 256, 0, dev->stream>>>(fptr(src), a, total, (int)cols);
+    split_cols_kernel<<<dim3((unsigned)((cols + 255) / 256), (unsigned)(rows < 65535 ? rows : 65535)), 256, 0, dev->stream>>>(fptr(src), a, rows, (int)cols);
     CC_LAUNCH_CHECK(dev);
     return CC_OK;
 }

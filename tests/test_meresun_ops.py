@@ -192,7 +192,7 @@ class Mixer:
         return out
 
 
-@pytest.mark.parametrize("H,dn,dr,dv,qr,kr,window", [(3, 8, 4, 10, 12, 20, 7), (1, 16, 2, 5, 6, 9, 1), (8, 32, 16, 48, 64, 96, 40), (6, 4, 8, 3, 10, 33, 200), (64, 2, 2, 2, 8, 6, 5)])
+@pytest.mark.parametrize("H,dn,dr,dv,qr,kr,window", [(3, 8, 4, 10, 12, 20, 7), (1, 16, 2, 5, 6, 9, 1), (8, 32, 16, 48, 64, 96, 40), (6, 4, 8, 3, 10, 33, 200), (64, 2, 2, 2, 8, 6, 5), (16, 4, 4, 40, 8, 36, 50), (4, 6, 2, 70, 8, 12, 3)])
 def test_latent_attention_whole_and_in_portions(dev, H, dn, dr, dv, qr, kr, window):
     rng = np.random.default_rng(H * 7 + window)
     D, T = 24, 61
