@@ -155,7 +155,10 @@ struct Runner : csr_runner {
             if (r.add_embedding) { x0 = x.dup(); break; }
         for (size_t ri = 0; ri < runs.size(); ri++) {
             const Layer& L = layers[runs[ri].layer];
-            if (runs[ri].add_embedding) x = std::move(x).add_inplace(x0);
+            if (runs[ri].add_embedding) {            // (not add_inplace: like the reference's CPU code it skips a tail of len % 4 elements)
+                cc_view xv = x.view(), ev = x0.view();
+                check(cc_gated_sum(dev, &xv, 1, &ev, nullptr, nullptr, nullptr, nullptr, nullptr));
+            }
             {
                 CudaTensor h = norm(x, L.norm1, conf.norm_groups);
                 std::vector<CudaTensor> part;

@@ -154,7 +154,8 @@ CudaTensor czr_runner_impl::feed_forward(const Layer& L, const CudaTensor& x) {
         cc_view h1v = h1.view(), h2v = h2.view();
         check(cc_glu_inplace(dev, &h1v, &h2v, CC_ACT_SILU));
         CudaTensor sh = L.s_down.matmul_vec(h1);
-        y = std::move(y).add_inplace(sh);
+        cc_view yv = y.view(), sv = sh.view();      // (not add_inplace: like the reference's CPU code it skips a tail of len % 4 elements)
+        check(cc_gated_sum(dev, &yv, 1, &sv, nullptr, nullptr, nullptr, nullptr, nullptr));
     }
     return y;
 }

@@ -92,6 +92,8 @@ CONFIGS = {
     "many_experts": config([attn_layer(window=64, mlp=moe_cfg(experts=16, top=5, groups=4, keep=2, ff=12, shared=40))], width=64, vocab=128),
     "wide_key_narrow_value": config([delta_layer(heads=2, kv_heads=1, dim=64, vdim=6, conv=5), delta_layer(heads=4, kv_heads=4, dim=128, vdim=10, conv=2, mlp=None)], width=56),
     "only_attention_window_one": config([attn_layer(window=1, mlp=None), attn_layer(window=2, kv_from=0, mlp=None)], width=32),
+    "width_not_a_multiple_of_four": config([delta_layer(heads=2, kv_heads=1, dim=9, vdim=7, mlp=moe_cfg(experts=4, top=2, groups=2, keep=1, ff=5, shared=11)),
+                                            attn_layer(heads=2, kv_heads=2, dim=6, vdim=5, window=10, mlp=moe_cfg(experts=3, top=1, groups=1, keep=1, ff=7, shared=3))], width=15, vocab=21),
     "aligned_for_tensor_cores": config([delta_layer(heads=2, kv_heads=1, dim=64, vdim=64, mlp=moe_cfg(experts=4, top=2, groups=2, keep=1, ff=64, shared=128)),
                                         attn_layer(heads=2, kv_heads=1, dim=64, vdim=64, window=20)], width=128, vocab=256),
 }
