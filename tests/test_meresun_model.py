@@ -178,6 +178,48 @@ def test_random_configurations(dev, seed):
     m.close()
 
 
+def random_aligned_config(seed):
+    """sizes a real model could have in small (multiples of 8 and 16), so that the tensor-core products, the grouped expert products and
+    passes of several tiles all run"""
+    rng = np.random.default_rng(2000 + seed)
+    width = int(rng.choice([64, 128, 192, 256]))
+    layers = []
+    for _ in range(int(rng.integers(2, 5))):
+        rd = int(rng.choice([8, 16, 32]))
+        kind = rng.choice(["dense", "moe"])
+        if kind == "moe":
+            g = int(rng.choice([1, 2, 4])); per = int(rng.choice([2, 4])); keep = int(rng.integers(1, g + 1))
+            mlp = moe(experts=g * per, top=int(rng.integers(1, min(4, keep * per) + 1)), groups=g if g > 1 else 0, keep=keep, ff=int(rng.choice([32, 64, 96])), limit=float(rng.uniform(1.0, 4.0)))
+        else:
+            mlp = dense(ff=int(rng.choice([64, 192, 320, 512])))
+        layers.append(layer(heads=int(rng.choice([2, 4, 6, 8, 12])), dim=int(rng.choice([16, 32, 48, 64])), rot_dim=rd, vdim=int(rng.choice([16, 32, 48, 64])),
+                            q_rank=int(rng.choice([32, 64, 96, 128])), kv_rank=int(rng.choice([32, 64, 96, 128, 160])), window=int(rng.choice([16, 40, 100, 129])),
+                            scale=float(rng.uniform(0.05, 0.3)), mlp=mlp, rotary=rot(rd, base=2.5e5, scaling={"factor": 4.0, "original": 128, "fast": 16.0, "slow": 1.0})))
+    n = len(layers)
+    a = int(rng.integers(0, n)); b = int(rng.integers(a + 1, n + 1))
+    return config(layers, width=width, vocab=int(rng.choice([96, 256, 577])), groups=int(rng.choice([1, 2, 4])), side=int(rng.choice([8, 16, 32])),
+                  loop=(a, b, int(rng.integers(2, 4))), embed_scale=0.5)
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_aligned_configurations(dev, seed):
+    conf = random_aligned_config(seed)
+    rng = np.random.default_rng(seed)
+    c = meresun.parse_config(conf)
+    toks = rng.integers(0, c["vocab"], 300).tolist()
+    c, w, m = build(dev, conf, seed, "float32", chunk=128)
+    want = R.forward(conf, w, toks)
+    for portions in ([300], [130, 41, 2, 127], [260] + [1] * 40):
+        err = rel_err(run_portions(m, toks, portions), want)
+        assert err.max() < TOL["float32"], (seed, portions, err.max())
+    m.close()
+    c, w, m = build(dev, conf, seed, "bfloat16", chunk=128)
+    for portions in ([300], [33, 200, 67], [260] + [1] * 40):
+        err = rel_err(run_portions(m, toks, portions), want)
+        assert np.median(err) < TOL["bfloat16"] / 2 and (err > TOL["bfloat16"]).mean() <= 0.05, (seed, portions, np.median(err), err.max())
+    m.close()
+
+
 def test_a_model_without_gates_and_sinks(dev):
     conf = config([layer(), layer(mlp=moe())])
     c, w, m = build(dev, conf, 22, drop=(".rg1", ".rg1.b", ".rg2", ".rg2.b", ".sink"))
