@@ -1053,7 +1053,7 @@ struct SplitArgs {
     int end[SPLIT_MAX];          // first column behind part p
     int n;
 };
-// grid (ceil(cols / 256), min(rows, 65535)): a thread owns one column (its part is found once) and walks the rows of its grid line
+// grid (ceil(cols / 256), about rows / 8): a thread owns one column (its part is found once) and walks the rows of its grid line
 __global__ void split_cols_kernel(const float* __restrict__ src, SplitArgs a, int64_t rows, int cols) {
     const int c = blockIdx.x * 256 + threadIdx.x;
     if (c >= cols) return;
@@ -1085,7 +1085,8 @@ extern "C" CC_API int cc_split_cols(cc_device* dev, const cc_view* src, int32_t 
     }
     const int64_t total = rows * cols;
     if (total == 0) return CC_OK;
-    split_cols_kernel<<<dim3((unsigned)((cols + 255) / 256), (unsigned)(rows < 65535 ? rows : 65535)), 256, 0, dev->stream>>>(fptr(src), a, rows, (int)cols);
+    const int64_t lines = (rows + 7) / 8;             // a thread copies about 8 rows of its column
+    split_cols_kernel<<<dim3((unsigned)((cols + 255) / 256), (unsigned)(lines < 65535 ? lines : 65535)), 256, 0, dev->stream>>>(fptr(src), a, rows, (int)cols);
     CC_LAUNCH_CHECK(dev);
     return CC_OK;
 }
