@@ -1,6 +1,6 @@
 // mega.cu -- one persistent kernel per token ("megakernel") for the fused decode path: the variant whose weight stream runs through
-// REGISTERS (two segments per warp in flight, look-ahead prefetch across the grid barrier).  Since round 2 the default is the variant in
-// mega_ring.cu (weights through a TMA-fed shared-memory ring: DESIGN.md section 4.5); this one is the fallback (CRABML_MEGA_FLAGS without
+// REGISTERS (two segments per warp in flight, look-ahead prefetch across the grid barrier).  The default is the variant in
+// mega_ring.cu (weights through a TMA-fed shared-memory ring); this one is the fallback (CRABML_MEGA_FLAGS without
 // MK_F_RING, or a phase table whose working area leaves the ring fewer than 12 slots) and the A/B baseline.  The phase bodies both
 // kernels share live in mega_phases.cuh; the host side at the bottom of this file serves both.
 //

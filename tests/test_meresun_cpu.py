@@ -9,7 +9,7 @@ import pytest
 from crabml_b200 import meresun, models, rotary
 from crabml_b200.capi import TensorError
 from tests import meresun_ref as R
-from tests.meresun_common import config, dense, layer, mixed_config, moe, rot
+from tests.meresun_common import config, layer, mixed_config, moe, rot
 
 
 def test_parse_config_fills_defaults_and_rejects_unknowns():
@@ -52,7 +52,7 @@ def test_registry_knows_the_family(tmp_path):
     assert models.architecture_of(str(tmp_path)) == "Meresun"
 
 
-@pytest.mark.parametrize("r", [rot(16), rot(8, base=250000.0, scaling={"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}), rot(6, scaling=None),
+@pytest.mark.parametrize("r", [rot(16), rot(8, base=5e5, scaling={"factor": 2.5, "original": 1000, "fast": 20.0, "slow": 0.5}), rot(6, scaling=None),
                                rot(2, base=50.0), rot(64, base=1e6, scaling={"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0})])
 def test_frequency_tables_against_the_reference(r):
     f, mag = rotary.table_of(r)
@@ -64,12 +64,12 @@ def test_frequency_tables_against_the_reference(r):
 
 
 def test_yarn_keeps_fast_pairs_and_slows_the_slow_ones():
-    r = rot(32, base=10000.0, scaling={"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0})
+    r = rot(32, base=10000.0, scaling={"factor": 5.0, "original": 1024, "fast": 32.0, "slow": 1.0})
     f, mag = R.rotary_frequencies(r)
     plain, _ = R.rotary_frequencies({"dims": 32, "base": 10000.0})
     turns = 1024 * plain / (2 * np.pi)
-    assert np.allclose(f[turns > 40], plain[turns > 40]) and np.allclose(f[turns < 0.7], plain[turns < 0.7] / 4.0)
-    assert np.all(np.diff(f / plain) <= 1e-12) and mag == pytest.approx(0.1 * np.log(4.0) + 1.0)
+    assert np.allclose(f[turns > 40], plain[turns > 40]) and np.allclose(f[turns < 0.7], plain[turns < 0.7] / 5.0)
+    assert np.all(np.diff(f / plain) <= 1e-12) and mag == pytest.approx(0.1 * np.log(5.0) + 1.0)
 
 
 # ---- the reference pinned by hand ------------------------------------------------------------------------------------------------------
@@ -134,7 +134,7 @@ def test_ref_expert_clamps_gate_above_only_and_up_both_sides():
 
 
 def test_ref_layer_runs_follow_the_loop():
-    c = config([layer()] * 5, loop=(1, 3, 3))
-    assert R.layer_runs(c) == [(0, False), (1, False), (2, False), (1, True), (2, False), (1, True), (2, False), (3, False), (4, False)]
+    c = config([layer()] * 5, loop=(2, 4, 3))
+    assert R.layer_runs(c) == [(0, False), (1, False), (2, False), (3, False), (2, True), (3, False), (2, True), (3, False), (4, False)]
     assert R.layer_runs(config([layer()] * 2)) == [(0, False), (1, False)]
     assert R.layer_runs(config([layer()] * 2, loop=(0, 2, 2))) == [(0, False), (1, False), (0, True), (1, False)]
