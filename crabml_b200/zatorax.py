@@ -21,8 +21,8 @@ import numpy as np
 from . import capi
 from .capi import CudaError, TensorError
 from .safetensors import bf16_to_f32, f32_to_bf16, read_safetensors, write_safetensors  # noqa: F401  (also this module's names)
-from .seqmodel import SeqModel
-from .tensor import CudaTensor, CudaTensorDevice
+from .seqmodel import SeqModel, Uploader, handle_of
+from .tensor import CudaTensorDevice
 
 ARCHITECTURE = "Zatorax"
 MIXERS = {"delta": 0, "attention": 1}
@@ -124,51 +124,17 @@ def random_weights(conf: dict, seed: int = 0, scale: float = 1.0) -> dict:
 
 # ---- the model on a device ------------------------------------------------------------------------------------------------------------
 class ZatoraxModel(SeqModel):
-    """Weights of one model on one device + its runner (sequences, steps and generation: seqmodel.SeqModel).  `weights`: {name: float32 ndarray} (values representable in bfloat16 when
-    dtype == "bfloat16") or the pair read_safetensors returns."""
+    """Weights of one model on one device + its runner (sequences, steps and generation: seqmodel.SeqModel).  `weights`: {name: float32
+    ndarray} (values representable in bfloat16 when dtype == "bfloat16") or the pair read_safetensors returns."""
 
     def __init__(self, device: CudaTensorDevice, conf: dict, weights, dtype: str = "bfloat16", chunk: int = 0):
-        if dtype not in ("bfloat16", "float32"):
-            raise TensorError(f"dtype must be bfloat16 or float32, not {dtype!r}")
         self.device, self.conf, self.dtype = device, parse_config(conf), dtype
-        bf16_names = set()
-        if isinstance(weights, tuple):
-            weights, bf16_names = weights
-        want = expected_tensors(self.conf)
-        missing = [n for n in want if n not in weights]
-        if missing:
-            raise TensorError(f"model is missing {len(missing)} tensors, first: {missing[0]}")
-        for n, shape in want.items():
-            if list(np.asarray(weights[n]).shape) != list(shape):
-                raise TensorError(f"tensor {n}: shape {list(np.asarray(weights[n]).shape)} in the file, {list(shape)} by the config")
-
-        def f32(name):
-            a = weights[name]
-            return bf16_to_f32(a) if name in bf16_names else np.asarray(a, np.float32)
-
-        def vec(name):                                                     # small parameters: always f32 on the device
-            a = np.ascontiguousarray(f32(name), np.float32).reshape(-1)
-            return CudaTensor.from_cpu(a, [a.size], capi.F32, device)
-
-        def mat_from(a32, bits16):                                         # a product's matrix: bf16 or f32 by the mode
-            shape = list(a32.shape if a32 is not None else bits16.shape)
-            if dtype == "float32":
-                return CudaTensor.from_cpu(np.ascontiguousarray(a32 if a32 is not None else bf16_to_f32(bits16), np.float32), shape, capi.F32, device)
-            return CudaTensor.from_cpu(np.ascontiguousarray(bits16 if bits16 is not None else f32_to_bf16(a32)), shape, capi.BF16, device)
-
-        def mat(name):
-            a = weights[name]
-            return mat_from(None, np.asarray(a)) if name in bf16_names else mat_from(np.asarray(a, np.float32), None)
-
-        def stack(names):
-            arrs = [weights[n] for n in names]
-            if all(n in bf16_names for n in names):
-                return mat_from(None, np.concatenate([np.asarray(a) for a in arrs], 0))
-            return mat_from(np.concatenate([f32(n) for n in names], 0), None)
+        up = Uploader(device, weights, dtype)
+        up.check(expected_tensors(self.conf))
+        vec, mat, stack = up.vec, up.mat, up.stack
 
         c = self.conf
-        self.tensors = {"embed": CudaTensor.from_cpu(np.ascontiguousarray(f32("embed")), [c["vocab"], c["width"]], capi.F32, device),
-                        "final.norm": vec("final.norm"), "head": mat("head")}
+        self.tensors = {"embed": up.mat32("embed"), "final.norm": vec("final.norm"), "head": mat("head")}
         lcs = (capi.czr_layer_config * len(c["layers"]))()
         lws = (capi.czr_layer_weights * len(c["layers"]))()
         for i, L in enumerate(c["layers"]):
@@ -182,7 +148,7 @@ class ZatoraxModel(SeqModel):
                 for k in ("q", "k", "v", "b", "a", "g", "o"):
                     t[k] = mat(p + "mix." + k)
                 for k in ("q", "k", "v"):
-                    t[k + "_conv"] = CudaTensor.from_cpu(np.ascontiguousarray(f32(f"{p}mix.{k}.conv")), list(weights[f"{p}mix.{k}.conv"].shape), capi.F32, device)
+                    t[k + "_conv"] = up.mat32(f"{p}mix.{k}.conv")
                 t["a_log"], t["dt_bias"], t["out_norm"] = vec(p + "mix.A_log"), vec(p + "mix.dt_bias"), vec(p + "mix.norm")
             else:
                 lc.window, lc.scale = m["mask"]["size"], m["scale"]
@@ -197,7 +163,7 @@ class ZatoraxModel(SeqModel):
                 lc.experts, lc.top, lc.groups, lc.keep_groups, lc.expert_ff = r["experts"], r["top"], r["groups"]["count"], r["groups"]["keep"], mlp["expert"]["ff"]
                 lc.shared_ff = mlp["shared"]["ff"] if mlp["shared"] else 0
                 t["norm2"] = vec(p + "norm2")
-                t["router"] = CudaTensor.from_cpu(np.ascontiguousarray(f32(p + "mlp.router")), [r["experts"], c["width"]], capi.F32, device)
+                t["router"] = up.mat32(p + "mlp.router")
                 t["correction"] = vec(p + "mlp.correction")
                 for part, key in (("gate", "e_gate"), ("up", "e_up"), ("down", "e_down")):
                     t[key] = stack([f"{p}mlp.e{e}.{part}" for e in range(r["experts"])])
@@ -205,7 +171,7 @@ class ZatoraxModel(SeqModel):
                     for part in ("gate", "up", "down"):
                         t["s_" + part] = mat(f"{p}mlp.shared.{part}")
             for k, v in t.items():
-                setattr(lws[i], k, v.buf.handle.value if hasattr(v.buf.handle, 'value') else v.buf.handle)
+                setattr(lws[i], k, handle_of(v))
                 self.tensors[f"{p}{k}"] = v                                  # keep alive
         cc = capi.czr_config(len(c["layers"]), c["width"], c["vocab"], c["norm"]["eps"], int(chunk))
         h = C.c_void_p()
